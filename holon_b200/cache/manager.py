@@ -1,7 +1,8 @@
 """The cache manager: pages of keys and values with a block table per request, in groups; request slots; state of
 fixed size per request.
 
-A group is a set of cache entries whose mixers asked for the same thing (`PagedKV`: heads, head size, window). One
+A group is a set of cache entries whose mixers asked for the same thing (`PagedKV`: heads, head size, window; or
+`PagedLatent`: one latent row per token that all heads read). One
 page number of a group names the same page in each of its entries, so a request has one block-table row per group.
 Groups have pools of their own, sized to hold the same number of tokens
 (core/holon/core/memory.py:327-330; core/holon/core/assembly.py:140-189). A page goes back to its pool when its
@@ -43,13 +44,12 @@ class CacheGroup:
         self.first = np.zeros(max_seqs + 1, dtype=np.int64)       # first logical page still held
         self.count = np.zeros(max_seqs + 1, dtype=np.int64)       # logical pages reserved so far
         self.dirty: set[int] = set()
-        self.kv = torch.zeros((len(entries), pages + 1, 2, decl.kv_heads, page_size, decl.head_dim), dtype=dtype,
-                              device=device)
+        self.kv = torch.zeros((len(entries), pages + 1, *decl.page_shape(page_size)), dtype=dtype, device=device)
         self.table_device = torch.from_numpy(self.table).to(device)
 
     @staticmethod
     def page_bytes(decl: PagedKV, entries: int, page_size: int, itemsize: int) -> int:
-        return entries * 2 * decl.kv_heads * page_size * decl.head_dim * itemsize
+        return entries * math.prod(decl.page_shape(page_size)) * itemsize
 
     def need(self, slot: int, tokens: int) -> int:
         return max(0, math.ceil(tokens / self.page_size) - int(self.count[slot]))

@@ -1,4 +1,5 @@
-"""One registry from an architecture's name (`config.json`: `architectures[0]`) to its typed configuration and recipe.
+"""One registry from an architecture's name (`config.json`: `architectures[0]`, or the string `architecture`) to its
+typed configuration and recipe.
 
 The reference resolves `arch.<name>` to exactly one model plugin and refuses duplicates
 (core/holon/core/plugins.py:31-66, 207-212); this registry keeps both rules in one process.
@@ -45,8 +46,11 @@ def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
     """The architecture `config.json` names. Importing `holon_b200.models` registers the built-in ones."""
     from .. import models  # noqa: F401  (registration on import)
     names = config.get("architectures")
+    if names is None and isinstance(config.get("architecture"), str):
+        names = [config["architecture"]]
     if not isinstance(names, (list, tuple)) or not names:
-        raise ConfigError("config.json: 'architectures' must be a list with the model class's name first")
+        raise ConfigError("config.json: 'architectures' must be a list with the model class's name first "
+                          "(or 'architecture' that name)")
     if names[0] not in _ARCHITECTURES:
         raise ConfigError(f"config.json: architecture {names[0]!r} is not registered; known: {list(architectures())}")
     return _ARCHITECTURES[names[0]]

@@ -32,9 +32,11 @@ class PartRef:
 
 @dataclasses.dataclass(frozen=True)
 class LayerSpec:
+    """`ffn` None: the layer has a mixer only."""
+
     block: PartRef
     mixer: PartRef
-    ffn: PartRef
+    ffn: PartRef | None
     norm: PartRef
 
 

@@ -20,7 +20,8 @@ class Param:
     fills: a merged projection lists its stored halves there, a plain tensor lists itself.
 
     `kind`: "matrix" (a product's weight, stored [out, in], kept in the engine's dtype), "gain" (a norm's weight:
-    kept in the engine's dtype unless the file stores 32 bits, which stay 32 bits) or "table" (embedding rows)."""
+    kept in the engine's dtype unless the file stores 32 bits, which stay 32 bits), "table" (embedding rows) or
+    "coef" (a few coefficients of a 32-bit computation: always kept in 32 bits)."""
 
     def __init__(self, name: str, shape: tuple[int, ...], kind: str, pieces: dict[str, tuple[int, int]] | None = None):
         self.name, self.shape, self.kind = name, tuple(shape), kind
@@ -78,6 +79,24 @@ class PagedKV:
     kv_heads: int
     head_dim: int
     window: int = 0
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        """One page of one cache entry: keys, then values, per kv head."""
+        return (2, self.kv_heads, page_size, self.head_dim)
+
+
+@dataclasses.dataclass(frozen=True)
+class PagedLatent:
+    """One row per token, in pages, that all heads read: a latent of `rank` numbers from which a mixer makes every
+    head's keys and values, then `rot_dim` numbers of a rotated key part that the heads share. Nothing per head is
+    kept. `window` as for PagedKV."""
+
+    rank: int
+    rot_dim: int
+    window: int = 0
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (page_size, self.rank + self.rot_dim)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -144,6 +163,10 @@ class Residual:
     def __init__(self, h: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.h, self.delta = h, delta
         self.normed, self.normed_by = None, None
+
+    def final_rows(self, norm, index: torch.Tensor) -> torch.Tensor:
+        """The rows `index` of what the last block left, under the model's last norm (what the head reads)."""
+        return norm.gather(self, index)
 
 
 class Scaled:

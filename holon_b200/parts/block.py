@@ -9,14 +9,16 @@ from .base import BuildContext, Link, Part, Residual
 
 
 class PreNorm(Part):
-    def __init__(self, ctx: BuildContext, *, layer: int, hidden: int, mixer: PartRef, ffn: PartRef,
+    def __init__(self, ctx: BuildContext, *, layer: int, hidden: int, mixer: PartRef, ffn: PartRef | None,
                  norm: PartRef) -> None:
         super().__init__()
         self.ctx = ctx
         self.input_norm = self.add_child("input_norm", ctx.part(norm, dim=hidden))
         self.mixer = self.add_child("mixer", ctx.part(mixer, layer=layer, hidden=hidden))
-        self.post_norm = self.add_child("post_norm", ctx.part(norm, dim=hidden))
-        self.ffn = self.add_child("ffn", ctx.part(ffn, layer=layer, hidden=hidden))
+        self.post_norm = self.ffn = None                             # (a layer may have a mixer only)
+        if ffn is not None:
+            self.post_norm = self.add_child("post_norm", ctx.part(norm, dim=hidden))
+            self.ffn = self.add_child("ffn", ctx.part(ffn, layer=layer, hidden=hidden))
 
     def forward(self, stream: Residual, step, cache, after=None) -> Residual:
         """`after`: the block that runs next (None: none, or unknown). For the few rows of a decode step the
@@ -24,6 +26,9 @@ class PreNorm(Part):
         the feed-forward the sum and `after`'s input norm (see base.Link), where the part that reads those rows can
         take them unscaled."""
         x = self.input_norm.add(stream)
+        if self.ffn is None:
+            stream.delta = self.mixer.forward(x, step, cache)
+            return stream
         step.link = self._offer(stream, step, self.post_norm, self.ffn)
         stream.delta = self.mixer.forward(x, step, cache)
         step.link = None                                             # (an offer nobody took lapses)

@@ -1,0 +1,79 @@
+"""Routed experts: each token runs `top` of `experts` small feed-forwards, chosen by a router.
+
+    z = W_router x (32-bit),  s = softmax(z) over all experts,  chosen = the `top` largest s,
+    weight_e = s_e · scale (with `renormalize`: divided by the chosen ones' sum first),
+    y = Σ_chosen weight_e · W_down,e act(W_up,e x)  +  sigmoid(w_sg · x) · W_down,s act(W_up,s x)   (the shared expert, if any)
+
+`activation`: "relu2" (the square of relu) or "silu". The tokens are not sorted on the host: the router's kernel
+counts the tokens of each expert, a scan lays the (token, choice) pairs out expert by expert, the two products run
+over those rows tile by tile (every tile of one expert's weight), and a last kernel adds each token's `top` rows in
+the order of its choices, so the sum does not depend on what else is in the batch.
+
+The experts' weights are stacked: up [experts · inter, hidden], down [experts · hidden, inter]; the router's rows
+and the shared expert's gate row are one product with 32-bit output.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, Part
+from .linear import Linear
+
+ACTIVATIONS = {"relu2": 1, "silu": 2}
+
+
+class Experts(Part):
+    def __init__(self, ctx: BuildContext, *, experts: int, top: int, scale: float, inter: int, hidden: int,
+                 shared_inter: int | None = None, activation: str = "relu2", renormalize: bool = False,
+                 layer: int = 0) -> None:
+        super().__init__()
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"experts: activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+        if not 1 <= top <= experts:
+            raise ValueError(f"experts: top {top} of {experts} experts")
+        self.ctx, self.experts, self.top, self.scale, self.inter, self.hidden = ctx, experts, top, float(scale), inter, hidden
+        self.act, self.renormalize, self.shared_inter = ACTIVATIONS[activation], bool(renormalize), shared_inter
+        pieces = {"router": experts}
+        if shared_inter:
+            pieces["shared.sg"] = 1
+        self.router = self.add_child("route", Linear(ctx, "weight", hidden, pieces))
+        self.up = self.add_param("up", (experts * inter, hidden), "matrix",
+                                 {f"e{e}.up": (e * inter, (e + 1) * inter) for e in range(experts)})
+        self.down = self.add_param("down", (experts * hidden, inter), "matrix",
+                                   {f"e{e}.down": (e * hidden, (e + 1) * hidden) for e in range(experts)})
+        self.shared_up = self.shared_down = None
+        if shared_inter:
+            self.shared_up = self.add_child("shared_up", Linear(ctx, "weight", hidden, {"shared.up": shared_inter}))
+            self.shared_down = self.add_child("shared_down", Linear(ctx, "weight", shared_inter, {"shared.down": hidden}))
+
+    def loadables(self, prefix: str = ""):
+        """Stored names: router, e<j>.up, e<j>.down, shared.up, shared.down, shared.sg."""
+        for name, p, rows in super().loadables(prefix):
+            for child in ("route.", "shared_up.", "shared_down."):
+                if name.startswith(prefix + child):
+                    name = prefix + name[len(prefix + child):]
+            yield name, p, rows
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        t, k, ctx, e, top = x.shape[0], self.ctx.kernels, self.ctx, self.experts, self.top
+        z = self.router.forward(x, out_dtype=torch.float32)             # [t, experts (+ 1)]: router logits, gate
+        chosen = ctx.empty(t, top, dtype=torch.int32)
+        weight = ctx.empty(t, top, dtype=torch.float32)
+        counts = torch.zeros(2 * e + 1, dtype=torch.int32, device=ctx.device)   # per expert: tokens, then first row (+ end)
+        k.route_top(chosen, weight, counts, z, e, self.scale, self.renormalize)
+        place = ctx.empty(t * top, dtype=torch.int32)                    # the row of each (token, choice)
+        token_of = ctx.empty(t * top, dtype=torch.int32)                 # the token of each row
+        k.expert_rows(place, token_of, counts, chosen, e)
+        starts = counts[e:]
+        act = ctx.empty(t * top, self.inter)
+        k.expert_linear(act, x, token_of, self.up.tensor.view(e, self.inter, self.hidden), starts, self.act)
+        y = ctx.empty(t * top, self.hidden)
+        k.expert_linear(y, act, None, self.down.tensor.view(e, self.hidden, self.inter), starts, 0)
+        shared = None
+        if self.shared_up is not None:
+            hs = self.shared_up.forward(x)
+            k.activation(hs, self.act)
+            shared = self.shared_down.forward(hs)
+        out = ctx.empty(t, self.hidden)
+        k.expert_combine(out, y, place, weight, shared, z if shared is not None else None, e)
+        return out

@@ -8,7 +8,7 @@ import dataclasses
 import torch
 
 from ..config.spec import ModelSpec
-from .base import BuildContext, PagedKV, Part, SlotState
+from .base import BuildContext, PagedKV, PagedLatent, Part, SlotState
 
 
 @dataclasses.dataclass(frozen=True)
@@ -17,7 +17,7 @@ class CacheEntry:
 
     entry: int
     layer: int
-    decl: PagedKV | None
+    decl: PagedKV | PagedLatent | None
     slot_states: tuple[SlotState, ...]
 
 
@@ -94,4 +94,4 @@ class Model(Part):
         """Logits [R, V] in 32-bit of the step's tokens `index` (int32 [R]) from the trunk's residual stream."""
         if index.shape[0] == 0:
             return None
-        return self.head.forward(self.norm.gather(stream, index))
+        return self.head.forward(stream.final_rows(self.norm, index))

@@ -6,7 +6,8 @@ the rows of one parameter (merged projections, build.py:372-424 with std/holon_s
 not stop at the first one: one `WeightError` lists the missing names, the unexpected ones and the wrong shapes.
 
 Precision: products' weights and tables take the engine's dtype; a norm weight that the file stores in 32 bits stays
-32-bit even under a bfloat16 engine; integer tensors become int32.
+32-bit even under a bfloat16 engine; coefficients of 32-bit computations (kind "coef") are always 32-bit; integer
+tensors become int32.
 """
 from __future__ import annotations
 
@@ -66,7 +67,7 @@ class NameMap:
 def _dtype_for(kind: str, stored: torch.dtype, engine: torch.dtype) -> torch.dtype:
     if not stored.is_floating_point:
         return torch.int32
-    if kind == "gain" and stored == torch.float32:
+    if kind == "coef" or (kind == "gain" and stored == torch.float32):
         return torch.float32
     return engine
 

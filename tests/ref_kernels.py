@@ -148,3 +148,119 @@ class RefKernels:
             c = q.cumsum(-1)
             i = int(torch.searchsorted(c, torch.tensor([u * float(c[-1])], dtype=c.dtype), right=True)[0])
             tokens[r] = min(i, q.numel() - 1)
+
+    # ---- hyper-connections, latent attention, routed experts
+
+    def hyper_mix_norm(self, out, xs, src, y, mix, outc, inc, weight, eps, offset, index):
+        """Old streams: xs [T, S, H], or src [T, H] standing for every stream. New ones: Σ_s mix[s, t] old_s +
+        outc[t] y (y None: the old ones). Without index they are written to xs. out = norm(Σ_t inc[t] new_t)."""
+        rows = slice(None) if index is None else index.long()
+        s = xs.shape[1]
+        old = xs[rows] if src is None else src[rows][:, None, :].expand(-1, s, -1)
+        new = old
+        if y is not None:
+            new = torch.einsum("st,nsh->nth", mix.float(), old) + outc.float()[None, :, None] * y[rows].float()[:, None, :]
+        if index is None:
+            xs.copy_(new)
+        u = new.sum(1) if inc is None else torch.einsum("t,nth->nh", inc.float(), new)
+        self.rmsnorm(out, u, weight, eps, offset)
+
+    @staticmethod
+    def _turn(x, cs, dims):
+        half = dims // 2
+        cos, sin = cs[..., :half], cs[..., half:]
+        a, b, rest = x[..., :half], x[..., half:dims], x[..., dims:]
+        return torch.cat((a * cos - b * sin, b * cos + a * sin, rest), dim=-1)
+
+    def latent_prepare(self, qa, first, heads, dim, rot, rank, dkv_at, positions, table, rot_dims, norm_weight, eps,
+                       cache, write_index):
+        t, dt = first.shape[0], first.dtype
+        cs = table[positions.long()] if rot_dims else None
+        q_r = first[:, :heads * (dim + rot)].view(t, heads, dim + rot)[:, :, dim:].float()
+        if rot_dims:
+            q_r = self._turn(q_r, cs[:, None, :], rot_dims)
+        qa[:, :, rank:] = q_r.to(dt)
+        if dkv_at >= 0:
+            d = first[:, dkv_at:dkv_at + rank + rot].float()
+            c = d[:, :rank]
+            c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * norm_weight.float()
+            k_r = d[:, rank:]
+            if rot_dims:
+                k_r = self._turn(k_r, cs, rot_dims)
+            w = write_index.long()
+            ok = w >= 0
+            cache.view(-1, rank + rot)[w[ok]] = torch.cat((c, k_r), dim=-1).to(dt)[ok]
+
+    def linear_heads(self, out, x, w):
+        out.copy_(torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out.dtype))
+
+    def latent_attention(self, out, qa, cache, block_table, rows, scale, rank, window):
+        page_size = cache.shape[1]
+        out.zero_()
+        qs, slots, lens = rows.query_start.tolist(), rows.row_slot.tolist(), rows.kv_len.tolist()
+        for b in range(rows.n_rows):
+            s, e, n = qs[b], qs[b + 1], lens[b]
+            if n == 0 or s == e:
+                continue
+            pages = block_table[slots[b], : -(-n // page_size)].long()
+            kc = cache[pages].reshape(-1, cache.shape[2])[:n].float()
+            scores = torch.einsum("qhd,kd->hqk", qa[s:e].float(), kc) * scale
+            pos = torch.arange(n - (e - s), n)[:, None]
+            key = torch.arange(n)[None, :]
+            hidden = key > pos
+            if window > 0:
+                hidden = hidden | (pos - key >= window)
+            probs = scores.masked_fill(hidden, float("-inf")).softmax(-1)
+            out[s:e] = torch.einsum("hqk,kd->qhd", probs, kc[:, :rank]).to(out.dtype)
+
+    def sigmoid_gate(self, o, g):
+        o.copy_((o.float() * torch.sigmoid(g.float())).to(o.dtype))
+
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize):
+        s = torch.softmax(z[:, :experts].float(), dim=-1)
+        top = chosen.shape[1]
+        order = torch.argsort(-s, dim=-1, stable=True)[:, :top]           # equal scores: the lower expert first
+        w = torch.gather(s, 1, order)
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        chosen.copy_(order.to(torch.int32))
+        weight.copy_(w * scale)
+        counts[:experts] += torch.bincount(order.reshape(-1), minlength=experts).to(torch.int32)
+
+    def expert_rows(self, place, token_of, counts, chosen, experts):
+        """counts[experts:] = first row of each expert and the end; pairs laid out expert by expert."""
+        t, top = chosen.shape
+        starts = torch.zeros(experts + 1, dtype=torch.int64)
+        starts[1:] = torch.cumsum(counts[:experts].long(), 0)
+        counts[experts:] = starts.to(torch.int32)
+        order = torch.argsort(chosen.reshape(-1).long(), stable=True)
+        place[order] = torch.arange(t * top, dtype=torch.int32)
+        token_of.copy_((order // top).to(torch.int32))
+
+    @staticmethod
+    def _act(x, act):
+        if act == 1:
+            return torch.relu(x) ** 2
+        if act == 2:
+            return torch.nn.functional.silu(x)
+        return x
+
+    def expert_linear(self, out, x, token_of, w, starts, act):
+        st = starts.tolist()
+        for e in range(w.shape[0]):
+            a, b = st[e], st[e + 1]
+            if b > a:
+                rows = x[token_of[a:b].long()] if token_of is not None else x[a:b]
+                out[a:b] = self._act(rows.float() @ w[e].float().T, act).to(out.dtype)
+
+    def activation(self, x, act):
+        x.copy_(self._act(x.float(), act).to(x.dtype))
+
+    def expert_combine(self, out, y, place, weight, shared, z, experts):
+        t, top = weight.shape
+        acc = torch.zeros(out.shape, dtype=torch.float32)
+        for k in range(top):
+            acc += weight[:, k:k + 1] * y[place.view(t, top)[:, k].long()].float()
+        if shared is not None:
+            acc += torch.sigmoid(z[:, experts:experts + 1].float()) * shared.float()
+        out.copy_(acc.to(out.dtype))

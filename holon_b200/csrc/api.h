@@ -101,6 +101,55 @@ int hb_attention_tcgen05_status(unsigned int* status);
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.
 int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k, hb_stream stream);
 
+// `batch` float32 products at once, one per head: out[t, b, :] = x[t, b, :] · w[b]ᵀ with w [batch, n, k]; row t of
+// product b starts at x + t * ldx + b * x_batch and at out + t * ldo + b * o_batch (elements).
+int hb_gemm_f32_heads(float* out, const float* x, const float* w, int m, int n, int k, int batch, long ldx, long x_batch,
+                      long ldo, long o_batch, hb_stream stream);
+
+// Hyper-connections (csrc/hyper.cu). Row r reads token t = index ? index[r] : r. Old streams: xs [tokens, streams,
+// dim] (32-bit), or, with src [tokens, dim], that row for every stream. With y [tokens, dim] (out's dtype):
+// new_q = sum_s mix[s * streams + q] old_s + outc[q] y, else new = old. Without index the new streams are written to
+// xs. out [rows, dim] = RMSNorm(sum_q inc[q] new_q) (inc null: ones) · (weight + offset). 1 to 16 streams.
+int hb_hyper_mix_norm(void* out, int out_dtype, float* xs, const float* src, const void* y, const float* mix,
+                      const float* outc, const float* inc, const void* weight, int weight_dtype, float eps, float offset,
+                      const int32_t* index, int rows, int dim, int streams, hb_stream stream);
+
+// Latent attention (csrc/latent.cu, csrc/latent_bf16.cu). The cache holds one row per token, [latent (rank) | rotated
+// key part (rot)], in pages [pages, page_size, rank + rot]; queries are folded per head: qa [tokens, heads, rank + rot].
+// hb_latent_prepare: `first` [tokens, ld] holds per head [dim unrotated | rot rotated] query entries from column 0 and,
+// from column dkv_at (< 0: none), the down-projection's rank + rot outputs. Writes the rotated query parts into
+// qa[:, :, rank:] (the first rot_dims entries turn, half-split pairs, angles from table [max_positions, rot_dims],
+// cosines then sines) and, with dkv_at >= 0, [RMSNorm(latent) · norm_weight | rotated key part] into cache row
+// write_index[t] (negative or out of range: skipped).
+int hb_latent_prepare(void* qa, const void* first, int dtype, int ld, int tokens, int heads, int dim, int rot, int rank,
+                      int dkv_at, const int32_t* positions, const float* table, int rot_dims, int max_positions,
+                      const void* norm_weight, int weight_dtype, float eps, void* cache, const int32_t* write_index,
+                      int pages, int page_size, hb_stream stream);
+// out [tokens, heads, rank] = softmax_j(scale · qa · row_j) · latent_j over the keys a query sees (as hb_attention_generic).
+int hb_latent_attention_generic(void* out, const void* qa, const void* cache, int dtype, const int32_t* block_table,
+                                int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                const int32_t* kv_len, int rows, int tokens, int heads, int rank, int rot, int pages,
+                                int page_size, float scale, int window, hb_stream stream);
+
+// Routed experts (csrc/experts.cu). z [tokens, ld]: 32-bit router logits in columns 0 .. experts - 1. chosen / weight
+// [tokens, top]: the experts with the largest softmax scores (equal ones by ascending expert) and score · scale
+// (renormalize: divided by the chosen scores' sum first); counts[e] += 1 per choice. hb_expert_rows: counts
+// [2 experts + 1] -> counts[experts + e] = first row of expert e (and the end); place[token * top + k] = the pair's
+// row, token_of[row] = its token. hb_expert_linear: out [rows, n] = act(x[token_of ? token_of[row] : row] · w[e]ᵀ) for
+// the rows of expert e, w [experts, n, k]; act 0 none, 1 relu squared, 2 silu. hb_expert_combine: out [tokens, hidden] =
+// sum_k weight[t, k] · y[place[t, k]] + (shared ? sigmoid(z[t, gate_at]) · shared[t] : 0).
+int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, int ld, int tokens, int experts,
+                 int top, float scale, int renormalize, hb_stream stream);
+int hb_expert_rows(int32_t* place, int32_t* token_of, int32_t* counts, const int32_t* chosen, int tokens, int top,
+                   int experts, hb_stream stream);
+int hb_expert_linear(void* out, const void* x, int dtype, const int32_t* token_of, const void* w, const int32_t* starts,
+                     int rows, int experts, int n, int k, int act, hb_stream stream);
+int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight, const void* shared,
+                      const float* z, int ldz, int gate_at, int tokens, int top, int hidden, hb_stream stream);
+// x = act(x) in place (act as above); o [tokens, n] *= sigmoid(g[t * ld + i]).
+int hb_activation(void* x, int dtype, long count, int act, hb_stream stream);
+int hb_sigmoid_gate(void* o, const void* g, int dtype, int tokens, int n, long ld, hb_stream stream);
+
 // bfloat16 product for at most 16 rows of x, bound by reading w once. mode 0: out [m, n] (bfloat16, or float32 when
 // out_f32) = x [m, k] · w [n, k]ᵀ. mode 1: w is [2 inter, k], gate rows first; out [m, inter] = silu(x · gateᵀ) ·
 // (x · upᵀ). k a multiple of 8; pointers 16-byte aligned.

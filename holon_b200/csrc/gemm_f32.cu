@@ -9,7 +9,11 @@
 
 template <bool VEC>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ out, const float* __restrict__ x,
-                                                       const float* __restrict__ w, int m, int n, int k) {
+                                                       const float* __restrict__ w, int m, int n, int k, long ldx,
+                                                       long ldo, long x_batch, long o_batch) {
+    x += (size_t)blockIdx.z * x_batch;               // blockIdx.z: which of several products (w [batch, n, k])
+    out += (size_t)blockIdx.z * o_batch;
+    w += (size_t)blockIdx.z * n * k;
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -22,12 +26,12 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ out, 
         float xv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
         const int kk = k0 + lk;
         if (VEC) {
-            if (xr < m && kk < k) *(float4*)xv = *(const float4*)(x + (size_t)xr * k + kk);
+            if (xr < m && kk < k) *(float4*)xv = *(const float4*)(x + (size_t)xr * ldx + kk);
             if (wr < n && kk < k) *(float4*)wv = *(const float4*)(w + (size_t)wr * k + kk);
         } else {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                if (xr < m && kk + i < k) xv[i] = x[(size_t)xr * k + kk + i];
+                if (xr < m && kk + i < k) xv[i] = x[(size_t)xr * ldx + kk + i];
                 if (wr < n && kk + i < k) wv[i] = w[(size_t)wr * k + kk + i];
             }
         }
@@ -56,7 +60,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ out, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int c = n0 + tx * 4 + j;
-            if (c < n) out[(size_t)r * n + c] = acc[i][j];
+            if (c < n) out[(size_t)r * ldo + c] = acc[i][j];
         }
     }
 }
@@ -68,8 +72,25 @@ extern "C" int hb_gemm_f32(float* out, const float* x, const float* w, int m, in
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
     if (grid.y > 65535) HB_REFUSE("gemm_f32: %d rows are above the kernel's limit of %d", m, 65535 * BM);
     const bool vec = (k % 4 == 0) && (((uintptr_t)x | (uintptr_t)w) % 16 == 0);
-    if (vec) gemm_f32_kernel<true><<<grid, 256, 0, s>>>(out, x, w, m, n, k);
-    else gemm_f32_kernel<false><<<grid, 256, 0, s>>>(out, x, w, m, n, k);
+    if (vec) gemm_f32_kernel<true><<<grid, 256, 0, s>>>(out, x, w, m, n, k, k, n, 0, 0);
+    else gemm_f32_kernel<false><<<grid, 256, 0, s>>>(out, x, w, m, n, k, k, n, 0, 0);
     HB_LAUNCH_CHECK("gemm_f32");
+    return 0;
+}
+
+// `batch` products at once, one per head: out[t, b, :] = x[t, b, :] · w[b]ᵀ with w [batch, n, k]; row t of product b
+// starts at x + t * ldx + b * x_batch and out + t * ldo + b * o_batch (elements), so heads that lie side by side in
+// wider rows are read and written in place.
+extern "C" int hb_gemm_f32_heads(float* out, const float* x, const float* w, int m, int n, int k, int batch, long ldx,
+                                 long x_batch, long ldo, long o_batch, hb_stream stream) {
+    if (m == 0 || n == 0 || batch == 0) return 0;
+    if (k <= 0) HB_REFUSE("gemm_f32_heads: k = %d", k);
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM, batch);
+    if (grid.y > 65535 || batch > 65535) HB_REFUSE("gemm_f32_heads: %d rows, %d products are above the kernel's limits", m, batch);
+    const bool vec = (k % 4 == 0) && (ldx % 4 == 0) && (x_batch % 4 == 0) && (((uintptr_t)x | (uintptr_t)w) % 16 == 0);
+    if (vec) gemm_f32_kernel<true><<<grid, 256, 0, s>>>(out, x, w, m, n, k, ldx, ldo, x_batch, o_batch);
+    else gemm_f32_kernel<false><<<grid, 256, 0, s>>>(out, x, w, m, n, k, ldx, ldo, x_batch, o_batch);
+    HB_LAUNCH_CHECK("gemm_f32_heads");
     return 0;
 }

@@ -1,0 +1,114 @@
+// Hyper-connections: S copies of the residual per token, mixed by learned coefficients around every sublayer.
+// One kernel does what the residual sum and the norm do for a single stream: it folds the pending sublayer output y
+// into all streams at once (new_t = sum_s mix[s, t] old_s + out[t] y), writes them, reads them with the next
+// sublayer's coefficients (u = sum_t in[t] new_t) and leaves RMSNorm(u) for the next product. All in 32-bit; the
+// streams are 32-bit in memory. One block per row; u is kept in shared memory between the two passes.
+#include "common.cuh"
+
+#define HC_MAX_STREAMS 16
+
+struct hc_coef {
+    float mix[HC_MAX_STREAMS * HC_MAX_STREAMS];
+    float out[HC_MAX_STREAMS];
+    float in[HC_MAX_STREAMS];
+};
+
+template <typename TD, typename TW, int S>
+__global__ void hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const float* __restrict__ src,
+                                      const TD* __restrict__ y, const float* __restrict__ mix,
+                                      const float* __restrict__ outc, const float* __restrict__ inc,
+                                      const TW* __restrict__ weight, float eps, float offset,
+                                      const int32_t* __restrict__ index, int dim, int streams) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[33];
+    __shared__ hc_coef c;
+    const int n = S > 0 ? S : streams;
+    const int r = blockIdx.x;
+    const size_t t = index ? (size_t)index[r] : (size_t)r;
+    for (int i = threadIdx.x; i < n * n; i += blockDim.x) c.mix[i] = mix ? mix[i] : 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        c.out[i] = outc ? outc[i] : 0.f;
+        c.in[i] = inc ? inc[i] : 1.f;
+    }
+    __syncthreads();
+    const bool fold = y != nullptr, write = index == nullptr && (fold || src != nullptr);
+    float* xr = xs + t * (size_t)n * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float old[S > 0 ? S : HC_MAX_STREAMS];
+        if (src) {
+            const float v = src[t * dim + i];
+#pragma unroll
+            for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) old[s] = v;
+        } else {
+#pragma unroll
+            for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) old[s] = xr[(size_t)s * dim + i];
+        }
+        const float yv = fold ? to_f32(y[t * dim + i]) : 0.f;
+        float u = 0.f;
+#pragma unroll
+        for (int q = 0; q < (S > 0 ? S : HC_MAX_STREAMS); ++q) {
+            if (q >= n) break;
+            float v;
+            if (fold) {
+                v = 0.f;
+#pragma unroll
+                for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) v = fmaf(c.mix[s * n + q], old[s], v);
+                v = fmaf(c.out[q], yv, v);
+            } else {
+                v = old[q];
+            }
+            if (write) xr[(size_t)q * dim + i] = v;
+            u = fmaf(c.in[q], v, u);
+        }
+        row[i] = u;
+        ss += u * u;
+    }
+    const float rstd = rsqrtf(block_sum(ss, scratch) / (float)dim + eps);
+    TD* o = out + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TD>(row[i] * rstd * (to_f32(weight[i]) + offset));
+}
+
+template <typename TD, typename TW>
+static int hyper_launch(void* out, float* xs, const float* src, const void* y, const float* mix, const float* outc,
+                        const float* inc, const void* weight, float eps, float offset, const int32_t* index, int rows,
+                        int dim, int streams, cudaStream_t s) {
+    const int threads = dim >= 2048 ? 512 : dim >= 512 ? 256 : 128;
+    const size_t smem = (size_t)dim * sizeof(float);
+#define HC_GO(S_) hyper_mix_norm_kernel<TD, TW, S_><<<rows, threads, smem, s>>>((TD*)out, xs, src, (const TD*)y, mix, outc, \
+        inc, (const TW*)weight, eps, offset, index, dim, streams)
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaSuccess;
+        if (streams == 4) e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        else if (streams == 2) e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        else e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) HB_REFUSE("hyper_mix_norm: %d columns do not fit in shared memory", dim);
+    }
+    if (streams == 4) HC_GO(4);
+    else if (streams == 2) HC_GO(2);
+    else HC_GO(0);
+#undef HC_GO
+    HB_LAUNCH_CHECK("hyper_mix_norm");
+    return 0;
+}
+
+// Row r reads token t = index ? index[r] : r. Old streams: xs [tokens, streams, dim], or, with src [tokens, dim], that
+// row for every stream. With y [tokens, dim] (out's dtype): new_q = sum_s mix[s * streams + q] old_s + outc[q] y, else
+// new = old. Without index the new streams are written to xs. out [rows, dim] = RMSNorm(sum_q inc[q] new_q) (inc null:
+// ones) times (weight + offset).
+extern "C" int hb_hyper_mix_norm(void* out, int out_dtype, float* xs, const float* src, const void* y, const float* mix,
+                                 const float* outc, const float* inc, const void* weight, int weight_dtype, float eps,
+                                 float offset, const int32_t* index, int rows, int dim, int streams, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (streams < 1 || streams > HC_MAX_STREAMS) HB_REFUSE("hyper_mix_norm: %d streams; 1 to %d", streams, HC_MAX_STREAMS);
+    if (y && (!mix || !outc)) HB_REFUSE("hyper_mix_norm: a pending output needs its mix and out coefficients");
+    if (dim > 51200) HB_REFUSE("hyper_mix_norm: %d columns are above 51200", dim);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == HB_F32 && weight_dtype == HB_F32)
+        return hyper_launch<float, float>(out, xs, src, y, mix, outc, inc, weight, eps, offset, index, rows, dim, streams, s);
+    if (out_dtype == HB_BF16 && weight_dtype == HB_BF16)
+        return hyper_launch<bf16, bf16>(out, xs, src, y, mix, outc, inc, weight, eps, offset, index, rows, dim, streams, s);
+    if (out_dtype == HB_BF16 && weight_dtype == HB_F32)
+        return hyper_launch<bf16, float>(out, xs, src, y, mix, outc, inc, weight, eps, offset, index, rows, dim, streams, s);
+    HB_REFUSE("hyper_mix_norm: out dtype %d with weight dtype %d", out_dtype, weight_dtype);
+}

@@ -752,6 +752,121 @@ class CudaKernels:
         self.linear(gate_up, x, weight)
         self.silu_mul(out, gate_up)
 
+    # ------------------------------------------------------------------ hyper-connections, latent attention, experts
+    def hyper_mix_norm(self, out, xs, src, y, mix, outc, inc, weight, eps, offset, index) -> None:
+        self._check(out, xs, src, y, mix, outc, inc, weight, index)
+        t, streams, dim = xs.shape
+        rows = index.shape[0] if index is not None else t
+        if xs.dtype != torch.float32 or out.shape != (rows, dim) or weight.shape != (dim,):
+            raise KernelError("hyper_mix_norm: xs float32 [tokens, streams, dim], out [rows, dim], weight [dim]")
+        if (src is not None and (src.dtype != torch.float32 or src.shape != (t, dim))) \
+                or (y is not None and (y.shape != (t, dim) or y.dtype != out.dtype)):
+            raise KernelError("hyper_mix_norm: src float32 [tokens, dim], y [tokens, dim] of out's dtype")
+        for name, c, shape in (("mix", mix, (streams, streams)), ("out", outc, (streams,)), ("in", inc, (streams,))):
+            if c is not None and (c.dtype != torch.float32 or c.shape != shape):
+                raise KernelError(f"hyper_mix_norm: {name} must be float32 {shape}")
+        self._call("hb_hyper_mix_norm", self._p(out), _code(out), self._p(xs), self._p(src), self._p(y), self._p(mix),
+                   self._p(outc), self._p(inc), self._p(weight), _code(weight), ctypes.c_float(eps), ctypes.c_float(offset),
+                   self._i32(index, "index"), rows, dim, streams)
+
+    def latent_prepare(self, qa, first, heads, dim, rot, rank, dkv_at, positions, table, rot_dims, norm_weight, eps,
+                       cache, write_index) -> None:
+        self._check(qa, first, positions, table, norm_weight, cache, write_index)
+        t, ld = first.shape
+        if qa.shape != (t, heads, rank + rot) or qa.dtype != first.dtype or ld < heads * (dim + rot):
+            raise KernelError("latent_prepare: first [tokens, >= heads (dim + rot)], qa [tokens, heads, rank + rot], one dtype")
+        if table is not None and (table.dtype != torch.float32 or table.shape[1] != rot_dims):
+            raise KernelError("latent_prepare: the rotation table must be float32 [positions, rot_dims]")
+        if cache is not None and (cache.dtype != first.dtype or cache.dim() != 3 or cache.shape[2] != rank + rot):
+            raise KernelError("latent_prepare: cache must be [pages, page_size, rank + rot] of first's dtype")
+        self._call("hb_latent_prepare", self._p(qa), self._p(first), _code(first), ld, t, heads, dim, rot, rank, int(dkv_at),
+                   self._i32(positions, "positions"), self._p(table), int(rot_dims), table.shape[0] if table is not None else 0,
+                   self._p(norm_weight), _code(norm_weight) if norm_weight is not None else 0, ctypes.c_float(eps),
+                   self._p(cache), self._i32(write_index, "write_index"), cache.shape[0] if cache is not None else 0,
+                   cache.shape[1] if cache is not None else 1)
+
+    def linear_heads(self, out, x, w) -> None:
+        """out[t, b, :] = x[t, b, :] · w[b]ᵀ for every head b: x [tokens, heads, k] and out [tokens, heads, n] may be
+        views into wider rows (innermost stride 1), w [heads, n, k] contiguous. float32: the library's own kernel with
+        a fixed summation order; bfloat16: one batched product of cuBLAS through torch, as `linear` uses it."""
+        self._check(w)
+        t, b, k = x.shape
+        n = w.shape[1]
+        if w.shape != (b, n, k) or out.shape != (t, b, n) or not (out.dtype == x.dtype == w.dtype) \
+                or x.stride(2) != 1 or out.stride(2) != 1 or x.get_device() != self._index or out.get_device() != self._index:
+            raise KernelError(f"linear_heads: x {tuple(x.shape)} · w {tuple(w.shape)}ᵀ -> out {tuple(out.shape)} do not fit")
+        if t == 0:
+            return
+        if x.dtype == torch.float32:
+            self._call("hb_gemm_f32_heads", self._p(out), self._p(x), self._p(w), t, n, k, b,
+                       ctypes.c_long(x.stride(0)), ctypes.c_long(x.stride(1)), ctypes.c_long(out.stride(0)),
+                       ctypes.c_long(out.stride(1)))
+        else:
+            if self._pending:
+                self.flush()
+            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+
+    def latent_attention(self, out, qa, cache, block_table, rows, scale, rank, window) -> None:
+        self._check(out, qa, cache, block_table, rows.row_slot, rows.query_start, rows.kv_len)
+        t, heads, dk = qa.shape
+        if out.shape != (t, heads, rank) or cache.dim() != 3 or cache.shape[2] != dk or not (out.dtype == qa.dtype == cache.dtype):
+            raise KernelError("latent_attention: qa [tokens, heads, rank + rot], out [tokens, heads, rank], cache [pages, "
+                              "page_size, rank + rot], one dtype")
+        self._call("hb_latent_attention_generic", self._p(out), self._p(qa), self._p(cache), _code(qa),
+                   self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
+                   self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"), rows.n_rows, t, heads,
+                   rank, dk - rank, cache.shape[0], cache.shape[1], ctypes.c_float(scale), int(window))
+
+    def sigmoid_gate(self, o, g) -> None:
+        """o [tokens, n] *= sigmoid(g [tokens, n]); g may be a view into wider rows."""
+        self._check(o)
+        if g.shape != o.shape or g.dtype != o.dtype or g.stride(1) != 1 or g.get_device() != self._index:
+            raise KernelError("sigmoid_gate: g must have o's shape and dtype, innermost stride 1")
+        self._call("hb_sigmoid_gate", self._p(o), self._p(g), _code(o), o.shape[0], o.shape[1], ctypes.c_long(g.stride(0)))
+
+    def activation(self, x, act: int) -> None:
+        self._check(x)
+        self._call("hb_activation", self._p(x), _code(x), ctypes.c_long(x.numel()), int(act))
+
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize) -> None:
+        self._check(chosen, weight, counts, z)
+        t, top = chosen.shape
+        if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
+                or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 1:
+            raise KernelError("route_top: z float32 [tokens, >= experts], chosen int32 and weight float32 [tokens, top], "
+                              "counts int32 [2 experts + 1]")
+        self._call("hb_route_top", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"), self._p(z),
+                   z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)))
+
+    def expert_rows(self, place, token_of, counts, chosen, experts) -> None:
+        self._check(place, token_of, counts, chosen)
+        t, top = chosen.shape
+        if place.shape[0] != t * top or token_of.shape[0] != t * top or counts.shape[0] < 2 * experts + 1:
+            raise KernelError("expert_rows: place and token_of int32 [tokens * top], counts int32 [2 experts + 1]")
+        self._call("hb_expert_rows", self._i32(place, "place"), self._i32(token_of, "token_of"), self._i32(counts, "counts"),
+                   self._i32(chosen, "chosen"), t, top, int(experts))
+
+    def expert_linear(self, out, x, token_of, w, starts, act: int) -> None:
+        self._check(out, x, token_of, w, starts)
+        e, n, k = w.shape
+        rows = out.shape[0]
+        if out.shape != (rows, n) or x.shape[1] != k or not (out.dtype == x.dtype == w.dtype) or starts.shape[0] != e + 1 \
+                or (token_of is None and x.shape[0] != rows) or (token_of is not None and token_of.shape[0] != rows):
+            raise KernelError("expert_linear: x [*, k], w [experts, n, k], out [rows, n], starts int32 [experts + 1]")
+        self._call("hb_expert_linear", self._p(out), self._p(x), _code(x), self._i32(token_of, "token_of"), self._p(w),
+                   self._i32(starts, "starts"), rows, e, n, k, int(act))
+
+    def expert_combine(self, out, y, place, weight, shared, z, experts) -> None:
+        self._check(out, y, place, weight, shared, z)
+        t, hidden = out.shape
+        top = weight.shape[1]
+        if y.shape != (t * top, hidden) or y.dtype != out.dtype or place.shape[0] != t * top \
+                or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype or z is None
+                                            or z.dtype != torch.float32 or z.shape[1] <= experts)):
+            raise KernelError("expert_combine: y [tokens * top, hidden], shared [tokens, hidden], z float32 [tokens, > experts]")
+        self._call("hb_expert_combine", self._p(out), self._p(y), _code(out), self._i32(place, "place"), self._p(weight),
+                   self._p(shared), self._p(z), z.shape[1] if z is not None else 0, int(experts), t, top, hidden)
+
     def feed_tokens(self, token_ids, last_tokens, rows, from_last) -> None:
         """token_ids[first token of row r] = last_tokens[slot of row r] for the rows whose `from_last` is set."""
         self._check(token_ids, last_tokens, rows.row_slot, rows.query_start, from_last)

@@ -1,0 +1,151 @@
+"""Tiny Rulorax configurations, model folders with weights that make faults show, and the comparison with the plain
+implementation (tests/plain_rulorax.py) that the CPU and GPU tests of this design share."""
+from __future__ import annotations
+
+import json
+
+import torch
+from safetensors.torch import save_file
+
+import plain_rulorax as plain
+
+
+def _mixer(heads, dim, rot_dim, vdim, rank, base, sharpen, kv_from=None, rot_dims=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+         "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims},
+         "scale": sharpen / (dim + rot_dim) ** 0.5}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _moe(experts, top, scale, ff, shared=None):
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": scale}, "expert": {"ff": ff}}
+    if shared:
+        mlp["shared"] = {"ff": shared}
+    return mlp
+
+
+def _layer(mixer, mlp):
+    return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+
+
+# A: three streams; a dense layer, a layer that reads layer 0's latent, a layer with experts and no shared one, a layer
+# without a feed-forward that reads layer 2's latent. Sizes that are multiples of 16 (the tensor-core kernels' domain).
+RX_A = {"architecture": "Rulorax", "width": 64, "vocab": 211, "norm": {"eps": 1e-5}, "streams": 3, "layers": [
+    _layer(_mixer(3, 32, 16, 48, 32, 10000.0, 3.0), {"kind": "dense", "ff": 96}),
+    _layer(_mixer(3, 32, 16, 48, 32, 10000.0, 3.0, kv_from=0), _moe(6, 2, 1.5, 40, shared=56)),
+    _layer(_mixer(2, 16, 32, 16, 48, 300.0, 2.0), _moe(6, 3, 0.7, 24)),
+    _layer(_mixer(4, 16, 32, 32, 48, 300.0, 2.0, kv_from=2), None)]}
+# B: one stream; sizes that are multiples of nothing (head size 20, 12 rotated of which 8 turn, values of 28, rank 40,
+# width 72, an odd vocabulary), every expert chosen (top = experts), another eps.
+RX_B = {"architecture": "Rulorax", "width": 72, "vocab": 157, "norm": {"eps": 1e-6}, "streams": 1, "layers": [
+    _layer(_mixer(5, 20, 12, 28, 40, 1000000.0, 2.5, rot_dims=8), _moe(3, 3, 1.0, 36, shared=20)),
+    _layer(_mixer(5, 20, 12, 28, 40, 1000000.0, 2.5, kv_from=0, rot_dims=8), {"kind": "dense", "ff": 100}),
+    _layer(_mixer(1, 24, 8, 40, 24, 50.0, 2.0), _moe(9, 1, 3.0, 16, shared=8))]}
+# C: no hyper-connections (a plain residual); a larger latent (rank 128 + 64 rotated), eight heads.
+RX_C = {"architecture": "Rulorax", "width": 128, "vocab": 300, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_mixer(8, 64, 64, 64, 128, 10000.0, 3.0), _moe(8, 2, 2.5, 64, shared=64)),
+    _layer(_mixer(8, 64, 64, 64, 128, 10000.0, 3.0, kv_from=0), {"kind": "dense", "ff": 192})]}
+# D: five streams, two heads of different key and value sizes, one expert of which one is chosen.
+RX_D = {"architecture": "Rulorax", "width": 48, "vocab": 97, "norm": {"eps": 1e-5}, "streams": 5, "layers": [
+    _layer(_mixer(2, 48, 16, 16, 64, 5000.0, 3.0), _moe(1, 1, 1.0, 32)),
+    _layer(_mixer(2, 48, 16, 16, 64, 5000.0, 3.0), {"kind": "dense", "ff": 64})]}
+CONFIGS = {"a": RX_A, "b": RX_B, "c": RX_C, "d": RX_D}
+
+
+def tensor_table(config):
+    """(stored name, shape) of every tensor of a model folder, from config.json alone."""
+    w, out = config["width"], [("embed", (config["vocab"], config["width"])), ("final.norm", (config["width"],)),
+                               ("head", (config["vocab"], config["width"]))]
+    s = config.get("streams")
+    for i, layer in enumerate(config["layers"]):
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        out += [(p + "norm1", (w,)), (p + "mix.q", (m["heads"] * (m["dim"] + m["rot_dim"]), w)),
+                (p + "mix.uk", (m["heads"] * m["dim"], m["kv_rank"])), (p + "mix.uv", (m["heads"] * m["vdim"], m["kv_rank"])),
+                (p + "mix.g", (m["heads"] * m["vdim"], w)), (p + "mix.o", (w, m["heads"] * m["vdim"]))]
+        if "kv_from" not in m:
+            out += [(p + "mix.dkv", (m["kv_rank"] + m["rot_dim"], w)), (p + "mix.dkv.norm", (m["kv_rank"],))]
+        subs = ["hc1"]
+        if mlp is not None:
+            out.append((p + "norm2", (w,)))
+            subs.append("hc2")
+            if mlp["kind"] == "dense":
+                out += [(p + "mlp.gate", (mlp["ff"], w)), (p + "mlp.up", (mlp["ff"], w)), (p + "mlp.down", (w, mlp["ff"]))]
+            else:
+                ff = mlp["expert"]["ff"]
+                out.append((p + "mlp.router", (mlp["router"]["experts"], w)))
+                for e in range(mlp["router"]["experts"]):
+                    out += [(p + f"mlp.e{e}.up", (ff, w)), (p + f"mlp.e{e}.down", (w, ff))]
+                if mlp.get("shared"):
+                    sf = mlp["shared"]["ff"]
+                    out += [(p + "mlp.shared.up", (sf, w)), (p + "mlp.shared.down", (w, sf)), (p + "mlp.shared.sg", (1, w))]
+        if s:
+            for q in subs:
+                out += [(p + q + ".in", (s,)), (p + q + ".out", (s,)), (p + q + ".mix", (s, s))]
+    return out
+
+
+def make_weights(config, seed: int):
+    """Random weights, rounded to bfloat16 (so that both engines read the same numbers). Products' weights are
+    N(0, 1/in), so activations keep unit size and, with the configurations' scales, attention scores spread over
+    several units: single keys stand out and a wrong key, page or mask moves the logits visibly. Router rows are
+    N(0, 4/in): clear choices."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_table(config):
+        x = torch.randn(shape, generator=g, dtype=torch.float32)
+        if name.endswith((".in",)):
+            x = 1.0 / shape[0] + 0.2 * x
+        elif name.endswith(".out"):
+            x = 1.0 + 0.2 * x
+        elif name.endswith("hc1.mix") or name.endswith("hc2.mix"):
+            x = torch.eye(shape[0]) + 0.15 * x
+        elif len(shape) == 1:
+            x = 1.0 + 0.1 * x
+        elif name == "embed":
+            pass
+        elif name.endswith("router"):
+            x = 2.0 * x / shape[1] ** 0.5
+        else:
+            x = x / shape[1] ** 0.5
+        out[name] = x.to(torch.bfloat16).contiguous()
+    return out
+
+
+def make_folder(tmp_path, name: str, seed: int = 0, config=None):
+    config = config or CONFIGS[name]
+    folder = tmp_path / f"rulorax_{name}"
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file(make_weights(config, seed), str(folder / "model.safetensors"))
+    return folder
+
+
+def exact_logits(folder, ids):
+    config, weights = plain.read_folder(folder)
+    return plain.forward(config, weights, ids).float()
+
+
+# float32: the engine against the plain implementation in 64-bit, per row: the distance (mean taken off, root mean
+# square over the vocabulary) relative to the row's own spread. bfloat16: the same measure with the bound that rounding
+# of every product's output to 8 bits of mantissa over a handful of layers stays within; a wrong key, page, position or
+# expert moves a row of these sharpened models by its whole spread.
+LIMITS = {"float32": 2e-4, "bfloat16": 0.08}
+
+
+def row_error(got, want):
+    d = got.double() - want.double()
+    d = d - d.mean()
+    spread = (want.double() - want.double().mean()).pow(2).mean().sqrt()
+    return float(d.pow(2).mean().sqrt() / spread)
+
+
+def compare(got, want, dtype):
+    """`got`: {(request, position): logits row}; `want`: {request: exact logits [tokens, vocab]}."""
+    assert got, "nothing to compare"
+    worst = max((row_error(row, want[rid][pos]), rid, pos) for (rid, pos), row in got.items())
+    assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
+    if dtype == "float32":
+        for (rid, pos), row in got.items():
+            assert int(row.argmax()) == int(want[rid][pos].argmax()), (rid, pos)

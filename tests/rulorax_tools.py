@@ -127,11 +127,13 @@ def exact_logits(folder, ids):
     return plain.forward(config, weights, ids).float()
 
 
-# float32: the engine against the plain implementation in 64-bit, per row: the distance (mean taken off, root mean
-# square over the vocabulary) relative to the row's own spread. bfloat16: the same measure with the bound that rounding
-# of every product's output to 8 bits of mantissa over a handful of layers stays within; a wrong key, page, position or
-# expert moves a row of these sharpened models by its whole spread.
-LIMITS = {"float32": 2e-4, "bfloat16": 0.08}
+# The measure, per row: the distance from the plain implementation's 64-bit logits (mean taken off, root mean square
+# over the vocabulary) relative to the row's own spread. float32: every row within 2e-4 and every arg max the same.
+# bfloat16: rounding alone leaves rows of these models 0.005 to 0.02 away, except where it tips a router's close call
+# between two experts (a row in fifty, which then sits a few tenths away; rows after it are not carried along): at
+# least 94 rows in a hundred within 0.05 and the median within 0.025. A wrong key, page, position or expert moves
+# the rows it touches by their whole spread; faults that touch single rows are the kernel tests' business in bfloat16.
+LIMITS = {"float32": 2e-4, "bfloat16": 0.05}
 
 
 def row_error(got, want):
@@ -144,8 +146,13 @@ def row_error(got, want):
 def compare(got, want, dtype):
     """`got`: {(request, position): logits row}; `want`: {request: exact logits [tokens, vocab]}."""
     assert got, "nothing to compare"
-    worst = max((row_error(row, want[rid][pos]), rid, pos) for (rid, pos), row in got.items())
-    assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
+    errors = sorted((row_error(row, want[rid][pos]), rid, pos) for (rid, pos), row in got.items())
     if dtype == "float32":
+        worst = errors[-1]
+        assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
         for (rid, pos), row in got.items():
             assert int(row.argmax()) == int(want[rid][pos].argmax()), (rid, pos)
+        return
+    over = [e for e in errors if e[0] > LIMITS[dtype]]
+    assert len(over) <= max(1, 0.06 * len(errors)), f"{len(over)} of {len(errors)} rows are off, the worst {over[-1]}"
+    assert errors[len(errors) // 2][0] <= 0.025, f"the median row is {errors[len(errors) // 2][0]:.3g} of its spread off"

@@ -131,6 +131,16 @@ int hb_latent_attention_generic(void* out, const void* qa, const void* cache, in
                                 const int32_t* kv_len, int rows, int tokens, int heads, int rank, int rot, int pages,
                                 int page_size, float scale, int window, hb_stream stream);
 
+// The same on tensor cores in bfloat16 (csrc/latent_bf16.cu) for rows row0 .. row1 - 1 of the batch, which bring `tokens`
+// tokens in all, the first of them token `first_token` of the step; rank and rot multiples of 16, rank up to 512.
+// splits > 1: the keys of every row are cut into that many parts whose partial results go to scratch
+// (hb_latent_attention_scratch_floats(first_token + tokens, ...) floats) and are merged by a second kernel.
+size_t hb_latent_attention_scratch_floats(int tokens, int heads, int rank, int splits);
+int hb_latent_attention_bf16(void* out, float* scratch, const void* qa, const void* cache, const int32_t* block_table,
+                             int table_stride, const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len,
+                             int row0, int row1, int first_token, int tokens, int heads, int rank, int rot, int pages,
+                             int page_size, float scale, int window, int splits, hb_stream stream);
+
 // Routed experts (csrc/experts.cu). z [tokens, ld]: 32-bit router logits in columns 0 .. experts - 1. chosen / weight
 // [tokens, top]: the experts with the largest softmax scores (equal ones by ascending expert) and score · scale
 // (renormalize: divided by the chosen scores' sum first); counts[e] += 1 per choice. hb_expert_rows: counts

@@ -126,6 +126,7 @@ class CudaKernels:
         self.skinny32 = os.environ.get("HOLON_B200_SKINNY32", "1") != "0"
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
+        self.latent_split = None              # tests: a fixed number of key parts for one-token rows of latent attention
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
         # Decode steps: the products of a layer that follow one another on the same few rows (the mixer's last, the
         # feed-forward's two, the next mixer's first) can be queued and run in one launch; every other call of this table
@@ -812,10 +813,36 @@ class CudaKernels:
         if out.shape != (t, heads, rank) or cache.dim() != 3 or cache.shape[2] != dk or not (out.dtype == qa.dtype == cache.dtype):
             raise KernelError("latent_attention: qa [tokens, heads, rank + rot], out [tokens, heads, rank], cache [pages, "
                               "page_size, rank + rot], one dtype")
-        self._call("hb_latent_attention_generic", self._p(out), self._p(qa), self._p(cache), _code(qa),
-                   self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
-                   self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"), rows.n_rows, t, heads,
-                   rank, dk - rank, cache.shape[0], cache.shape[1], ctypes.c_float(scale), int(window))
+        rot = dk - rank
+        common = (self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
+                  self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"))
+        fast = qa.dtype == torch.bfloat16 and rank % 16 == 0 and rot % 16 == 0 and 16 <= rank <= 512 \
+            and self.attention_bf16 == "fast"
+        if not fast:                                  # float32, and sizes the tensor-core kernel does not take
+            return self._call("hb_latent_attention_generic", self._p(out), self._p(qa), self._p(cache), _code(qa), *common,
+                              rows.n_rows, t, heads, rank, rot, cache.shape[0], cache.shape[1], ctypes.c_float(scale),
+                              int(window))
+        sizes = (heads, rank, rot, cache.shape[0], cache.shape[1], ctypes.c_float(scale), int(window))
+        ones = rows.n_decode
+        if ones:                                      # rows of one token: their keys cut into parts that fill the GPU
+            splits = self.latent_splits(ones, heads, rank, rows.max_kv)
+            scratch = torch.empty(ones * heads * splits * (rank + 2), dtype=torch.float32, device=self.device) \
+                if splits > 1 else None
+            self._call("hb_latent_attention_bf16", self._p(out), self._p(scratch), self._p(qa), self._p(cache), *common,
+                       0, ones, 0, ones, *sizes, splits)
+        if rows.n_rows > ones:
+            self._call("hb_latent_attention_bf16", self._p(out), None, self._p(qa), self._p(cache), *common, ones,
+                       rows.n_rows, ones, t - ones, *sizes, 1)
+
+    def latent_splits(self, rows: int, heads: int, rank: int, max_kv: int) -> int:
+        """Parts the keys of one-token rows are cut into for the latent attention kernel: enough that two CTAs an SM
+        have work, each part at least two tiles of 64 keys, at most 32. A function of the batch's size and the longest
+        row only (under a CUDA graph: of the bucket its plan pinned)."""
+        if self.latent_split:                                            # (tests: a fixed number of parts)
+            return int(self.latent_split)
+        tile = 64 if rank <= 128 else 32 if rank <= 256 else 16          # (token, head) pairs a CTA
+        ctas = rows * (-(-heads // tile))
+        return max(1, min(32, -(-max_kv // 64) // 2, (2 * self.sms) // max(1, ctas)))
 
     def sigmoid_gate(self, o, g) -> None:
         """o [tokens, n] *= sigmoid(g [tokens, n]); g may be a view into wider rows."""

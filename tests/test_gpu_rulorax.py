@@ -145,9 +145,16 @@ def _paged(lens, page, rank, rot, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,rank,rot,page", [(4, 64, 32, 64), (3, 40, 12, 4), (16, 128, 64, 64), (1, 512, 64, 16), (5, 32, 16, 64), (24, 64, 16, 64)])
-def test_latent_attention(K, dtype, heads, rank, rot, page):
-    lens, new = [130, 1, 64, 65, 300, 7, 129], [1, 1, 64, 2, 37, 7, 1]
+@pytest.mark.parametrize("splits", [None, 3, 7])
+@pytest.mark.parametrize("heads,rank,rot,page", [(4, 64, 32, 64), (3, 40, 12, 4), (16, 128, 64, 64), (1, 512, 64, 16), (5, 32, 16, 64),
+                                                 (24, 64, 16, 64), (40, 256, 32, 64), (3, 144, 16, 16), (70, 80, 48, 64)])
+def test_latent_attention(K, dtype, heads, rank, rot, page, splits, monkeypatch):
+    """Rows of one token (short, at a tile's edge, long) beside portions of prompts; the bfloat16 kernel with the keys
+    of one-token rows whole, in 3 and in 7 parts (some of them empty for the short rows)."""
+    if splits and dtype == torch.float32:
+        pytest.skip("the 32-bit kernel does not cut the keys")
+    monkeypatch.setattr(K, "latent_split", splits)
+    lens, new = [130, 1, 64, 65, 300, 7, 129, 641], [1, 1, 64, 2, 37, 7, 1, 1]
     cache, table = _paged(lens, page, rank, rot, dtype, 5)
     rows = _rows(lens, new)
     t = sum(new)

@@ -298,3 +298,151 @@ extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int3
     HB_LAUNCH_CHECK("expert_combine");
     return 0;
 }
+
+// ---------------------------------------------------------------- the experts' products in bfloat16 on tensor cores
+// The same tiles (expert by expert, at most ceil(rows / BM) + experts of them), mma.sync m16n8k16 with 32-bit sums:
+// BM x 128 outputs a CTA of four warps, the k range in steps of 32 through a three-stage cp.async ring. x rows are
+// gathered by token_of while they are copied (rows past the expert's end are zero-filled), the weight tile is 128 rows
+// of w[e]. BM = 64 for prompts (many rows an expert), 16 for decode steps (a row or two an expert: the weight streams
+// once either way, and a 16-row tile wastes a quarter of the tensor work a 64-row tile would). k and n multiples of 8.
+#define XB_BN 128
+#define XB_BK 32
+#define XB_LD (XB_BK + 8)
+#define XB_STAGES 3
+
+__device__ __forceinline__ void xb_cp16(void* dst, const void* src, int bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void xb_ldsm4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void xb_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int BM>
+__global__ void __launch_bounds__(128) expert_linear_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ x,
+                                                                 const int32_t* __restrict__ token_of,
+                                                                 const bf16* __restrict__ w,
+                                                                 const int32_t* __restrict__ starts, int experts, int n,
+                                                                 int k, int act) {
+    constexpr int WARPS_M = BM == 64 ? 2 : 1, WARPS_N = 4 / WARPS_M;
+    constexpr int MF = BM / 16 / WARPS_M;                       // 16-row fragments a warp
+    constexpr int NF = XB_BN / 8 / WARPS_N;                     // 8-column fragments a warp
+    __shared__ __align__(16) bf16 as[XB_STAGES][BM][XB_LD];
+    __shared__ __align__(16) bf16 bs[XB_STAGES][XB_BN][XB_LD];
+    __shared__ int src[BM];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        int e = 0, r0 = 0, r1 = 0;
+        const bool ok = expert_tile(starts, experts, blockIdx.y, BM, e, r0, r1);
+        tile_info[0] = ok ? e : -1; tile_info[1] = r0; tile_info[2] = r1;
+    }
+    __syncthreads();
+    const int e = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
+    if (e < 0) return;
+    if (tid < BM) src[tid] = m0 + tid < m_end ? (token_of ? token_of[m0 + tid] : m0 + tid) : -1;
+    __syncthreads();
+    const int n0 = blockIdx.x * XB_BN;
+    const bf16* we = w + (size_t)e * n * k;
+    const int k_tiles = (k + XB_BK - 1) / XB_BK;
+
+    auto load = [&](int kt, int stage) {
+        const int k0 = kt * XB_BK;
+        for (int c = tid; c < (BM + XB_BN) * 4; c += 128) {      // 16-byte pieces: four a row
+            const int r = c >> 2, col = (c & 3) * 8;
+            const bool in_k = k0 + col < k;
+            if (r < BM) {
+                const int s = src[r];
+                const bool ok = s >= 0 && in_k;
+                xb_cp16(&as[stage][r][col], x + (ok ? (size_t)s * k + k0 + col : 0), ok ? 16 : 0);
+            } else {
+                const int wr = n0 + r - BM;
+                const bool ok = wr < n && in_k;
+                xb_cp16(&bs[stage][r - BM][col], we + (ok ? (size_t)wr * k + k0 + col : 0), ok ? 16 : 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+    float acc[MF][NF][4];
+#pragma unroll
+    for (int i = 0; i < MF; ++i)
+#pragma unroll
+        for (int j = 0; j < NF; ++j) { acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f; }
+
+#pragma unroll
+    for (int s = 0; s < XB_STAGES - 1; ++s) {
+        if (s < k_tiles) load(s, s); else asm volatile("cp.async.commit_group;\n" ::);
+    }
+    for (int kt = 0; kt < k_tiles; ++kt) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(XB_STAGES - 2));
+        __syncthreads();                                         // tile kt has landed; the stage of tile kt - 1 is free
+        if (kt + XB_STAGES - 1 < k_tiles) load(kt + XB_STAGES - 1, (kt + XB_STAGES - 1) % XB_STAGES);
+        else asm volatile("cp.async.commit_group;\n" ::);
+        const int stage = kt % XB_STAGES;
+#pragma unroll
+        for (int kk = 0; kk < XB_BK; kk += 16) {
+            uint32_t a[MF][4];
+#pragma unroll
+            for (int i = 0; i < MF; ++i)
+                xb_ldsm4(a[i], &as[stage][(wm * MF + i) * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int jp = 0; jp < NF / 2; ++jp) {
+                uint32_t b[4];
+                xb_ldsm4(b, &bs[stage][wn * NF * 8 + jp * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int i = 0; i < MF; ++i) {
+                    xb_mma(acc[i][2 * jp], a[i], b[0], b[1]);
+                    xb_mma(acc[i][2 * jp + 1], a[i], b[2], b[3]);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+    for (int i = 0; i < MF; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = m0 + (wm * MF + i) * 16 + (lane >> 2) + half * 8;
+            if (r >= m_end) continue;
+#pragma unroll
+            for (int j = 0; j < NF; ++j) {
+                const int c = n0 + wn * NF * 8 + j * 8 + (lane & 3) * 2;
+                if (c < n)
+                    *(__nv_bfloat162*)(out + (size_t)r * n + c) =
+                        __floats2bfloat162_rn(expert_act(acc[i][j][half * 2], act), expert_act(acc[i][j][half * 2 + 1], act));
+            }
+        }
+    }
+}
+
+// tile_rows: 16 or 64 rows a tile (0: chosen from the rows an expert gets on average).
+extern "C" int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w,
+                                     const int32_t* starts, int rows, int experts, int n, int k, int act, int tile_rows,
+                                     hb_stream stream) {
+    if (rows == 0 || n == 0) return 0;
+    if (k <= 0 || k % 8 || n % 8 || experts < 1) HB_REFUSE("expert_linear_bf16: k = %d and n = %d must be multiples of 8", k, n);
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) HB_REFUSE("expert_linear_bf16: pointers must be 16-byte aligned");
+    const int bm = tile_rows ? tile_rows : (rows <= 8 * experts ? 16 : 64);
+    if (bm != 16 && bm != 64) HB_REFUSE("expert_linear_bf16: tiles of %d rows; 16 or 64", bm);
+    const long tiles = (rows + bm - 1) / bm + experts;
+    if (tiles > 65535) HB_REFUSE("expert_linear_bf16: %d rows over %d experts are above the kernel's limit", rows, experts);
+    dim3 grid((n + XB_BN - 1) / XB_BN, (unsigned)tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bm == 16)
+        expert_linear_bf16_kernel<16><<<grid, 128, 0, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts,
+                                                           experts, n, k, act);
+    else
+        expert_linear_bf16_kernel<64><<<grid, 128, 0, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts,
+                                                           experts, n, k, act);
+    HB_LAUNCH_CHECK("expert_linear_bf16");
+    return 0;
+}

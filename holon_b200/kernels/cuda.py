@@ -127,6 +127,8 @@ class CudaKernels:
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.latent_split = None              # tests: a fixed number of key parts for one-token rows of latent attention
+        self.expert_products = "fast"         # "generic" forces the CUDA-core kernel for bfloat16 experts too (tests)
+        self.expert_tile_rows = 0             # tests: 16 or 64 rows a tile of the experts' tensor-core products (0: chosen)
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
         # Decode steps: the products of a layer that follow one another on the same few rows (the mixer's last, the
         # feed-forward's two, the next mixer's first) can be queued and run in one launch; every other call of this table
@@ -880,6 +882,10 @@ class CudaKernels:
         if out.shape != (rows, n) or x.shape[1] != k or not (out.dtype == x.dtype == w.dtype) or starts.shape[0] != e + 1 \
                 or (token_of is None and x.shape[0] != rows) or (token_of is not None and token_of.shape[0] != rows):
             raise KernelError("expert_linear: x [*, k], w [experts, n, k], out [rows, n], starts int32 [experts + 1]")
+        if x.dtype == torch.bfloat16 and k % 8 == 0 and n % 8 == 0 and self.expert_products == "fast" \
+                and (x.data_ptr() | w.data_ptr() | out.data_ptr()) % 16 == 0:
+            return self._call("hb_expert_linear_bf16", self._p(out), self._p(x), self._i32(token_of, "token_of"), self._p(w),
+                              self._i32(starts, "starts"), rows, e, n, k, int(act), int(self.expert_tile_rows))
         self._call("hb_expert_linear", self._p(out), self._p(x), _code(x), self._i32(token_of, "token_of"), self._p(w),
                    self._i32(starts, "starts"), rows, e, n, k, int(act))
 

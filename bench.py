@@ -55,6 +55,35 @@ QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
+def rulorax_config(width: int, heads: int, rank: int, rot: int, dim: int, vdim: int, dense_ff: int, experts: int, top: int,
+                   expert_ff: int, shared_ff: int, layers: int, vocab: int = 32768, streams: int = 4) -> dict:
+    """A Rulorax model for `--only rulorax`: layer 0 dense, the others routed experts with a shared one; every odd layer
+    reads the latent of the layer before it."""
+    def mixer(i):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "rot": {"base": 10000.0, "dims": rot},
+             "scale": (dim + rot) ** -0.5}
+        return dict(m, kv_from=i - 1) if i % 2 else m
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.0}, "expert": {"ff": expert_ff},
+           "shared": {"ff": shared_ff}}
+    return {"architecture": "Rulorax", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "streams": streams,
+            "layers": [{"type": "latent_attention", "mixer": mixer(i), "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe}
+                       for i in range(layers)]}
+
+
+# Sizes of layers that published latent-attention models with routed experts have (width, heads, latent rank, rotated
+# and unrotated head sizes, experts): "lite" a 16-billion-parameter model's (64 experts of 1,408, 6 chosen, latent 512),
+# "small" a 4-billion-parameter dense model's attention (latent 256) with small experts. Beside each the Qwen3 decoder
+# of the same width, heads and layers whose SwiGLU has as many active parameters a token.
+RULORAX_SIZES = {
+    "lite": (dict(width=2048, heads=16, rank=512, rot=64, dim=128, vdim=128, dense_ff=10944, experts=64, top=6, expert_ff=1408,
+                  shared_ff=2816, layers=6), dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=16, head_dim=128,
+                                                  intermediate_size=7552, num_hidden_layers=6, vocab_size=32768)),
+    "small": (dict(width=2560, heads=40, rank=256, rot=32, dim=64, vdim=64, dense_ff=6400, experts=32, top=4, expert_ff=1024,
+                   shared_ff=2048, layers=6), dict(hidden_size=2560, num_attention_heads=40, num_key_value_heads=8, head_dim=64,
+                                                   intermediate_size=4096, num_hidden_layers=6, vocab_size=32768)),
+}
+
+
 def _find_number(data, key: str):
     """The first number stored under `key` anywhere in a nested JSON value (a dict under the key: its "value")."""
     if isinstance(data, dict):
@@ -412,6 +441,129 @@ def sizes_run(args) -> dict:
     return out
 
 
+class TimedKernels:
+    """The kernel table with CUDA events around every call the parts make (the outermost ones: a method that calls
+    others is timed as a whole), for one eager step: microseconds by method."""
+
+    def __init__(self, kernels) -> None:
+        self._k, self._depth, self.records = kernels, 0, []
+
+    def __getattr__(self, name):
+        import torch
+        value = getattr(self._k, name)
+        if not callable(value) or name.startswith("_") or name in ("attention_capture_plan", "can_link", "flush", "status"):
+            return value
+
+        def timed(*a, **kw):
+            if self._depth:
+                return value(*a, **kw)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._depth += 1
+            start.record()
+            try:
+                return value(*a, **kw)
+            finally:
+                end.record()
+                self._depth -= 1
+                self.records.append((name, start, end))
+        return timed
+
+    def table(self) -> dict:
+        import torch
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, start, end in self.records:
+            calls, us = out.get(name, (0, 0.0))
+            out[name] = (calls + 1, us + start.elapsed_time(end) * 1e3)
+        self.records = []
+        return {name: {"calls": c, "us": round(us, 1)} for name, (c, us) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def step_tables(engine, batch: int, context: int, prompt: int) -> dict:
+    """Per-method microseconds of one eager prompt step (`prompt` tokens) and one eager decode step (`batch` rows that
+    hold `context` tokens), through the engine's own step function with `TimedKernels` in the kernel table's place."""
+    import torch
+    from holon_b200.engine.batch import StepEntry
+    built = engine.built
+    cache, runner, ctx = built.cache, built.runner, built.ctx
+    plain, timed = ctx.kernels, TimedKernels(ctx.kernels)
+    vocab = built.model.spec.vocab
+    out = {}
+
+    def run(entries, watch: bool):
+        ctx.kernels = timed if watch else plain
+        try:
+            runner.step(entries)
+        finally:
+            ctx.kernels = plain
+        return timed.table() if watch else None
+
+    slots = []
+    try:
+        slot = cache.admit()
+        slots.append(slot)
+        ids = prompts_of(vocab, 1, prompt, 5)[0]
+        cache.reserve(slot, prompt)
+        run([StepEntry(slot, ids, 0, [prompt - 1])], False)               # (warm-up: first use of every kernel)
+        cache.release(slots.pop())
+        slot = cache.admit()
+        slots.append(slot)
+        cache.reserve(slot, prompt)
+        out["prefill"] = run([StepEntry(slot, ids, 0, [prompt - 1])], True)
+        cache.release(slots.pop())
+        for i in range(batch):
+            slot = cache.admit()
+            slots.append(slot)
+            cache.reserve(slot, context)
+            run([StepEntry(slot, prompts_of(vocab, 1, context - 2, 9 + i)[0], 0, [])], False)
+        for watch in (False, True):
+            entries = [StepEntry(slot, [7], int(cache.computed[slot]), [0]) for slot in slots]
+            out["decode"] = run(entries, watch)
+    finally:
+        for slot in slots:
+            cache.release(slot)
+        torch.cuda.synchronize()
+    return out
+
+
+def rulorax_run(args) -> dict:
+    """Prefill and decode throughput of Rulorax at sizes that published models' layers have, beside the Qwen3 decoder of
+    the same width, heads, layers and active feed-forward parameters: one 2,048-token prompt; decode steps at batch 1
+    and 8 over 2,048-token contexts (through `Engine.step`, graphs on); and per-method microseconds of one eager step of
+    each kind. Random weights; rooflines are worked out from these numbers in the design notes."""
+    import gc
+    import torch
+    from holon_b200.engine import Engine, EngineConfig
+    from holon_b200.weights import RandomSource
+    out = {"only": "rulorax", "sizes": {}}
+    steps = max(8, min(args.steps, 32))
+    for name in (args.rulorax_sizes.split(",") if args.rulorax_sizes else RULORAX_SIZES):
+        ours, theirs = RULORAX_SIZES[name]
+        models = {"rulorax": rulorax_config(**ours), "qwen3": dict(QWEN3_8B, **theirs)}
+        result = {}
+        for which, cfg in models.items():
+            engine = Engine(EngineConfig(model=f"random weights, {which} {name}", device="cuda:0", dtype="bfloat16", page_size=64,
+                                         max_seqs=8, max_model_len=4096, max_step_tokens=4096, seed=0, prefix_cache=False,
+                                         state_memory=2 << 30),
+                            source=RandomSource(cfg, seed=6, device="cuda:0"))
+            arm = Arm(engine)
+            r = {"weights_gb": round(engine.built.weight_bytes / 1e9, 3)}
+            ms = prefill_run(arm, 2048, repeats=3, seed=100)
+            r["prefill"] = {"tokens": 2048, "ms": round(ms, 3), "tokens_per_s": round(2048 / ms * 1e3, 1)}
+            for b in (1, 8):
+                d = decode_run(arm, b, 2048 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+                r[f"decode_b{b}"] = {"ms_per_step": round(d["device_ms"] / steps, 4), "tokens_per_s": round(d["tokens"] / d["device_ms"] * 1e3, 1)}
+            if not args.no_kernels:
+                r["methods"] = step_tables(engine, 8, 2048, 2048)
+            result[which] = r
+            engine.close()
+            del engine, arm
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][name] = result
+    return out
+
+
 def shared_prompt_run(args) -> dict:
     """16 requests whose prompts share their first 2,048 tokens (64 tokens of their own follow), 32 tokens generated
     each, through `Engine.generate`, with the prefix cache and without it: seconds for all of them, second pass (the
@@ -520,6 +672,8 @@ def run_ours(args) -> dict:
         return sizes_run(args)
     if args.only == "shared_prompt":
         return shared_prompt_run(args)
+    if args.only == "rulorax":
+        return rulorax_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -642,12 +796,14 @@ def main() -> int:
                          "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
                          "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
                          "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
-                         "shared_prompt: 16 requests with a common 2,048-token beginning, with and without the prefix cache")
+                         "shared_prompt: 16 requests with a common 2,048-token beginning, with and without the prefix cache; "
+                         "rulorax: prefill and decode of the Rulorax design beside the Qwen3 decoder of equal size (--rulorax-sizes)")
     ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
+    ap.add_argument("--rulorax-sizes", default="", help="with --only rulorax: which sizes (lite, small; default both)")
     ap.add_argument("--no-points", action="store_true", help="leave out the points at other batch sizes and contexts")
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-kernel table")
     args = ap.parse_args()

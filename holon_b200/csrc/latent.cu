@@ -81,7 +81,7 @@ extern "C" int hb_latent_prepare(void* qa, const void* first, int dtype, int ld,
 
 // ---------------------------------------------------------------- attention on CUDA cores
 #define LAT_WARPS 4
-#define LAT_MAX_PER_LANE 16          // rank up to 512
+#define LAT_MAX_PER_LANE 32          // rank up to 1024
 
 template <typename T>
 __global__ void latent_attention_generic_kernel(T* __restrict__ out, const T* __restrict__ qa, const T* __restrict__ cache,

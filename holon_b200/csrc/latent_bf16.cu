@@ -4,16 +4,18 @@
 // All heads read the same cache rows [latent (rank) | rotated key part (rot)], so a request's (token, head) pairs are
 // the M side of one problem: its folded queries qa [tokens, heads, rank + rot] are contiguous rows of rank + rot, a
 // tile of them meets a tile of 64 cache rows once for the scores (over rank + rot) and once more, the same rows in
-// shared memory, for the values (their first `rank` numbers). A CTA has four warps. The output's `rank` columns are
-// cut into R = 1, 2 or 4 parts of up to 128; a warp owns 16 query rows and one part, so a CTA's tile is 64 / R rows,
-// the R warps of a row group compute the same scores and softmax (no exchange between warps) and each adds up its
-// own columns. Cache rows arrive by cp.async, two tiles in flight; rows past a request's length are zero-filled.
+// shared memory, for the values (their first `rank` numbers). A CTA has W = 4 warps (rows of one token: few query
+// rows, many CTAs) or 8 (prompt portions: a larger tile reads the cache rows once for twice the queries). The output's
+// `rank` columns are cut into R = 1, 2 or 4 parts of up to 128; a warp owns 16 query rows and one part, so a CTA's
+// tile is 16 W / R rows, the R warps of a row group hold the same scores and run the same softmax
+// and each adds up its own columns. (The scores themselves are shared out: each of the R warps multiplies the queries
+// with 64 / R of the tile's cache rows, and the group exchanges the results through shared memory.) Cache rows arrive by cp.async, two tiles in flight; rows past a request's length are zero-filled.
 // With `splits` > 1 (few query rows, many keys: decoding) a CTA takes one part of the key tiles and leaves its
 // running maximum, sum and unnormalised output in scratch; a second kernel merges the parts in a fixed order.
 #include "common.cuh"
 
 #define LB_BN 64                       // cache rows a tile
-#define LB_THREADS 128
+#define LB_SLD 68                      // floats a row of exchanged scores
 
 __device__ __forceinline__ void lb_cp16(void* dst, const void* src, int bytes) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -41,18 +43,20 @@ __device__ __forceinline__ uint32_t lb_pack(float lo, float hi) {
     return *(const uint32_t*)&v;
 }
 
-template <int R>
-__global__ void __launch_bounds__(LB_THREADS) latent_attention_bf16_kernel(
+template <int R, int W>
+__global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
         bf16* __restrict__ out, float* __restrict__ scratch, const bf16* __restrict__ qa, const bf16* __restrict__ cache,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int row1, int heads,
         int rank, int dk, int pages, int page_size, float scale, int window, int splits) {
-    constexpr int MT = 16 * (4 / R);                       // query rows a CTA
+    constexpr int MT = 16 * W / R;                         // query rows a CTA
+    constexpr int LB_THREADS = W * 32;
     extern __shared__ __align__(16) unsigned char lb_smem[];
     __shared__ long kb[2][LB_BN];                          // element offset of each cache row of a stage (-1: none)
     const int ld = dk + 8;                                 // shared-memory row stride: 16 bytes of padding a row
     bf16* qs = (bf16*)lb_smem;                             // [MT][ld]
     bf16* ks = qs + (size_t)MT * ld;                       // [2][LB_BN][ld]
+    float* sbuf = (float*)(ks + (size_t)2 * LB_BN * ld);   // [W / R][16][LB_SLD]: a row group's scores (R > 1)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     // which request and which tile of its (token, head) pairs
@@ -127,19 +131,44 @@ __global__ void __launch_bounds__(LB_THREADS) latent_attention_bf16_kernel(
         if (kt + 1 < my_end) { load_keys(kt + 1, stage ^ 1); lb_wait<1>(); } else { lb_wait<0>(); }
         __syncthreads();
         const bf16* kt_s = ks + (size_t)stage * LB_BN * ld;
-        // scores of this warp's 16 rows against the tile's 64 cache rows
+        // scores of this warp's 16 rows against the tile's 64 cache rows: each of the R warps of a row group takes
+        // 64 / R of the cache rows and the group exchanges the scores through shared memory
         float s[8][4];
+        {
+            constexpr int NP = 4 / R;                       // 16-row pairs of cache rows this warp scores
+            float sp[2 * NP][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-        for (int kk = 0; kk < dk; kk += 16) {
-            uint32_t a[4];
-            lb_ldsm4(a, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
+            for (int i = 0; i < 2 * NP; ++i) { sp[i][0] = sp[i][1] = sp[i][2] = sp[i][3] = 0.f; }
+            const int key0 = part * NP * 16;
+            for (int kk = 0; kk < dk; kk += 16) {
+                uint32_t a[4];
+                lb_ldsm4(a, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {
-                uint32_t bfr[4];
-                lb_ldsm4(bfr, kt_s + (size_t)(np * 16 + (lane & 7) + (lane >> 4) * 8) * ld + kk + ((lane >> 3) & 1) * 8);
-                lb_mma(s[2 * np], a, bfr[0], bfr[1]);
-                lb_mma(s[2 * np + 1], a, bfr[2], bfr[3]);
+                for (int q = 0; q < NP; ++q) {
+                    uint32_t bfr[4];
+                    lb_ldsm4(bfr, kt_s + (size_t)(key0 + q * 16 + (lane & 7) + (lane >> 4) * 8) * ld + kk + ((lane >> 3) & 1) * 8);
+                    lb_mma(sp[2 * q], a, bfr[0], bfr[1]);
+                    lb_mma(sp[2 * q + 1], a, bfr[2], bfr[3]);
+                }
+            }
+            if constexpr (R == 1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { s[i][0] = sp[i][0]; s[i][1] = sp[i][1]; s[i][2] = sp[i][2]; s[i][3] = sp[i][3]; }
+            } else {
+                float* sg = sbuf + (size_t)group * 16 * LB_SLD;
+#pragma unroll
+                for (int i = 0; i < 2 * NP; ++i) {
+                    const int col = key0 + i * 8 + (lane & 3) * 2;
+                    *(float2*)(sg + (size_t)(lane >> 2) * LB_SLD + col) = make_float2(sp[i][0], sp[i][1]);
+                    *(float2*)(sg + (size_t)((lane >> 2) + 8) * LB_SLD + col) = make_float2(sp[i][2], sp[i][3]);
+                }
+                asm volatile("bar.sync %0, %1;\n" ::"r"(1 + group), "r"(R * 32));      // the R warps of this row group
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 lo = *(const float2*)(sg + (size_t)(lane >> 2) * LB_SLD + i * 8 + (lane & 3) * 2);
+                    const float2 hi = *(const float2*)(sg + (size_t)((lane >> 2) + 8) * LB_SLD + i * 8 + (lane & 3) * 2);
+                    s[i][0] = lo.x; s[i][1] = lo.y; s[i][2] = hi.x; s[i][3] = hi.y;
+                }
             }
         }
         // mask, running maximum and sum (two rows a thread, four threads a row)
@@ -282,18 +311,20 @@ extern "C" int hb_latent_attention_bf16(void* out, float* scratch, const void* q
     if (splits < 1 || (splits > 1 && !scratch)) HB_REFUSE("latent attention: %d splits need scratch", splits);
     cudaStream_t s = (cudaStream_t)stream;
     const int r = rank <= 128 ? 1 : rank <= 256 ? 2 : 4;
-    const int mt = 16 * (4 / r);
+    const int warps = tokens > row1 - row0 ? 8 : 4;                     // (rows of several tokens: the larger tile)
+    const int mt = 16 * warps / r;
     const long pairs = (long)tokens * heads;
     const long tiles = (pairs + mt - 1) / mt + (row1 - row0);          // the most tiles any cut of the tokens into the rows has
     if (tiles > 0x7fffffffL || splits > 65535) HB_REFUSE("latent attention: %ld tiles, %d splits", tiles, splits);
-    const size_t smem = (size_t)(mt + 2 * LB_BN) * (dk + 8) * sizeof(bf16);
+    const size_t smem = (size_t)(mt + 2 * LB_BN) * (dk + 8) * sizeof(bf16) + (r > 1 ? (size_t)(warps / r) * 16 * LB_SLD * sizeof(float) : 0);
     dim3 grid((unsigned)tiles, (unsigned)splits);
-#define LB_GO(R_) do { \
-        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(latent_attention_bf16_kernel<R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        latent_attention_bf16_kernel<R_><<<grid, LB_THREADS, smem, s>>>((bf16*)out, scratch, (const bf16*)qa, (const bf16*)cache, \
+#define LB_GO(R_, W_) do { \
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(latent_attention_bf16_kernel<R_, W_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        latent_attention_bf16_kernel<R_, W_><<<grid, W_ * 32, smem, s>>>((bf16*)out, scratch, (const bf16*)qa, (const bf16*)cache, \
             block_table, table_stride, row_slot, query_start, kv_len, row0, row1, heads, rank, dk, pages, page_size, scale, window, splits); \
     } while (0)
-    if (r == 1) LB_GO(1); else if (r == 2) LB_GO(2); else LB_GO(4);
+    if (warps == 4) { if (r == 1) LB_GO(1, 4); else if (r == 2) LB_GO(2, 4); else LB_GO(4, 4); }
+    else { if (r == 1) LB_GO(1, 8); else if (r == 2) LB_GO(2, 8); else LB_GO(4, 8); }
 #undef LB_GO
     HB_LAUNCH_CHECK("latent_attention_bf16");
     if (splits > 1) {

@@ -842,7 +842,7 @@ class CudaKernels:
         row only (under a CUDA graph: of the bucket its plan pinned)."""
         if self.latent_split:                                            # (tests: a fixed number of parts)
             return int(self.latent_split)
-        tile = 64 if rank <= 128 else 32 if rank <= 256 else 16          # (token, head) pairs a CTA
+        tile = 64 if rank <= 128 else 32 if rank <= 256 else 16          # (token, head) pairs a CTA of four warps
         ctas = rows * (-(-heads // tile))
         return max(1, min(32, -(-max_kv // 64) // 2, (2 * self.sms) // max(1, ctas)))
 

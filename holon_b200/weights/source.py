@@ -4,7 +4,8 @@ Folder: `config.json` is required, every `*.safetensors` file is read in sorted 
 two files is an error (std/holon_std/weights/hf/source.py:49-115). Random: the reference has no such mode; its tests
 make tiny checkpoints with another library. Here every tensor is drawn from its own generator, seeded by
 (seed, stored name), so a tensor does not depend on which others are made, on their order, or on the device's
-memory: matrices and tables N(0, 0.02), norm weights 1 + N(0, 0.1).
+memory: matrices and tables N(0, 0.02), norm weights 1 + N(0, 0.1), coefficients of 32-bit computations (kind "coef")
+near neutral values: a square matrix I + N(0, 0.05), a vector of n entries 1/n + N(0, 0.05).
 """
 from __future__ import annotations
 
@@ -87,7 +88,11 @@ class RandomSource:
         for name, shape, kind in self.table():
             g = torch.Generator(device=self.device).manual_seed(_tensor_seed(self.seed, name))
             x = torch.randn(shape, generator=g, dtype=torch.float32, device=self.device)
-            x = x.mul_(self.STD_GAIN).add_(1.0) if kind == "gain" else x.mul_(self.STD_MATRIX)
+            if kind == "coef":
+                x = x.mul_(0.05)
+                x = x + (torch.eye(shape[0], device=self.device) if len(shape) == 2 and shape[0] == shape[1] else 1.0 / shape[0])
+            else:
+                x = x.mul_(self.STD_GAIN).add_(1.0) if kind == "gain" else x.mul_(self.STD_MATRIX)
             yield name, x.to(self.dtype)
 
 

@@ -152,6 +152,10 @@ int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z
                  int top, float scale, int renormalize, hb_stream stream);
 int hb_expert_rows(int32_t* place, int32_t* token_of, int32_t* counts, const int32_t* chosen, int tokens, int top,
                    int experts, hb_stream stream);
+// hb_route_top and hb_expert_rows as one call (one launch for up to 256 tokens and 1,024 experts). counts [2 experts + 3]
+// need not be zeroed; afterwards counts[2 experts + 1 ..] = (0, tokens): the `starts` of one expert that takes every token.
+int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of, const float* z, int ld,
+                  int tokens, int experts, int top, float scale, int renormalize, hb_stream stream);
 int hb_expert_linear(void* out, const void* x, int dtype, const int32_t* token_of, const void* w, const int32_t* starts,
                      int rows, int experts, int n, int k, int act, hb_stream stream);
 int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight, const void* shared,

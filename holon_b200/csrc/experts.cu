@@ -127,6 +127,106 @@ extern "C" int hb_expert_rows(int32_t* place, int32_t* token_of, int32_t* counts
     return 0;
 }
 
+// ---------------------------------------------------------------- choice and rows in one launch (few tokens)
+// One CTA of eight warps does what hb_route_top and hb_expert_rows do for up to RS_TOKENS tokens and RS_EXPERTS
+// experts: a warp routes a token at a time; counts, first rows and the pairs' rows are worked out in shared memory.
+// counts [2 experts + 3] is written whole: counts, first rows, the end, and the pair (0, tokens), which serves as the
+// `starts` of one expert that takes every token (the shared expert's product with its activation).
+#define RS_TOKENS 256
+#define RS_EXPERTS 1024
+__global__ void __launch_bounds__(256) route_rows_small_kernel(int32_t* __restrict__ chosen, float* __restrict__ weight,
+                                                               int32_t* __restrict__ counts, int32_t* __restrict__ place,
+                                                               int32_t* __restrict__ token_of, const float* __restrict__ z,
+                                                               int ld, int tokens, int experts, int top, float scale,
+                                                               int renormalize) {
+    extern __shared__ float rs_smem[];
+    float* sc = rs_smem;                                   // [8][experts]
+    int* cnt = (int*)(sc + 8 * (size_t)experts);           // [experts]: counts, then cursors
+    int* start = cnt + experts;                            // [experts + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    float* my = sc + (size_t)warp * experts;
+    for (int t = warp; t < tokens; t += 8) {
+        const float* zr = z + (size_t)t * ld;
+        float m = -INFINITY;
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, zr[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < experts; e += 32) { const float p = expf(zr[e] - m); my[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        __syncwarp();
+        const float inv = 1.f / sum;
+        float taken = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float bv = -1.f; int bi = 0x7fffffff;
+            for (int e = lane; e < experts; e += 32) { const float v = my[e]; if (v > bv) { bv = v; bi = e; } }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) {
+                chosen[(size_t)t * top + k] = bi;
+                weight[(size_t)t * top + k] = bv * inv;
+                my[bi] = -2.f;
+                atomicAdd(cnt + bi, 1);
+            }
+            taken += bv * inv;
+            __syncwarp();
+        }
+        const float f = renormalize ? scale / taken : scale;
+        for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= f;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) { start[e] = at; at += cnt[e]; }
+        start[experts] = at;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { counts[e] = cnt[e]; counts[experts + e] = start[e]; cnt[e] = 0; }
+    if (threadIdx.x == 0) { counts[2 * experts] = start[experts]; counts[2 * experts + 1] = 0; counts[2 * experts + 2] = tokens; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < tokens * top; i += blockDim.x) {
+        const int e = chosen[i];                            // (written by this block: visible after the barrier)
+        const int p = start[e] + atomicAdd(cnt + e, 1);
+        place[i] = p;
+        token_of[p] = i / top;
+    }
+}
+
+__global__ void expert_whole_kernel(int32_t* counts, int experts, int tokens) {
+    counts[2 * experts + 1] = 0;
+    counts[2 * experts + 2] = tokens;
+}
+
+// hb_route_top and hb_expert_rows as one call. counts [2 experts + 3] need not be zeroed; afterwards it also holds, at
+// 2 experts + 1, the pair (0, tokens).
+extern "C" int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of,
+                             const float* z, int ld, int tokens, int experts, int top, float scale, int renormalize,
+                             hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (experts < 1 || top < 1 || top > experts || ld < experts) HB_REFUSE("route_rows: top %d of %d experts in rows of %d", top, experts, ld);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (tokens <= RS_TOKENS && experts <= RS_EXPERTS) {
+        const size_t smem = ((size_t)8 * experts + 2 * experts + 1) * sizeof(float);
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(route_rows_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        route_rows_small_kernel<<<1, 256, smem, s>>>(chosen, weight, counts, place, token_of, z, ld, tokens, experts, top, scale, renormalize);
+        HB_LAUNCH_CHECK("route_rows_small");
+        return 0;
+    }
+    HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)(2 * experts + 3) * sizeof(int32_t), s));
+    int rc = hb_route_top(chosen, weight, counts, z, ld, tokens, experts, top, scale, renormalize, stream);
+    if (rc) return rc;
+    rc = hb_expert_rows(place, token_of, counts, chosen, tokens, top, experts, stream);
+    if (rc) return rc;
+    expert_whole_kernel<<<1, 1, 0, s>>>(counts, experts, tokens);
+    HB_LAUNCH_CHECK("expert_whole");
+    return 0;
+}
+
 // ---------------------------------------------------------------- the experts' products, any dtype, CUDA cores
 __device__ __forceinline__ float expert_act(float v, int act) {
     if (act == 1) { v = fmaxf(v, 0.f); return v * v; }            // the square of relu
@@ -264,17 +364,23 @@ extern "C" int hb_sigmoid_gate(void* o, const void* g, int dtype, int tokens, in
 }
 
 // ---------------------------------------------------------------- the weighted sum per token
+#define XC_TOP 64
 template <typename T>
 __global__ void expert_combine_kernel(T* __restrict__ out, const T* __restrict__ y, const int32_t* __restrict__ place,
                                       const float* __restrict__ weight, const T* __restrict__ shared,
                                       const float* __restrict__ z, int ldz, int gate_at, int top, int hidden) {
+    __shared__ int rows[XC_TOP];                            // the token's rows and weights, read once
+    __shared__ float wgt[XC_TOP];
     const size_t t = blockIdx.x;
+    const bool kept = top <= XC_TOP;
+    if (kept && threadIdx.x < top) { rows[threadIdx.x] = place[t * top + threadIdx.x]; wgt[threadIdx.x] = weight[t * top + threadIdx.x]; }
+    __syncthreads();
     const float gate = shared ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
-            const int p = place[t * top + k];
-            if (p >= 0) acc = fmaf(weight[t * top + k], to_f32(y[(size_t)p * hidden + i]), acc);
+            const int p = kept ? rows[k] : place[t * top + k];
+            if (p >= 0) acc = fmaf(kept ? wgt[k] : weight[t * top + k], to_f32(y[(size_t)p * hidden + i]), acc);
         }
         if (shared) acc = fmaf(gate, to_f32(shared[t * hidden + i]), acc);
         out[t * hidden + i] = from_f32<T>(acc);
@@ -286,7 +392,7 @@ extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int3
                                  hb_stream stream) {
     if (tokens == 0) return 0;
     if (shared && (!z || gate_at >= ldz)) HB_REFUSE("expert_combine: a shared expert needs its gate's logit");
-    const int threads = hidden >= 1024 ? 256 : 128;
+    const int threads = hidden >= 2048 ? 512 : hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == HB_F32)
         expert_combine_kernel<float><<<tokens, threads, 0, s>>>((float*)out, (const float*)y, place, weight,

@@ -267,28 +267,38 @@ __global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
     }
 }
 
-// One warp per (token, head) pair: the parts' results in the order of the parts.
-__global__ void latent_attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ scratch, long first_pair,
-                                              long pairs, int rank, int splits) {
-    const long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (i >= pairs) return;
-    const int lane = threadIdx.x & 31, width = rank + 2;
-    const float* p = scratch + (first_pair + i) * splits * width;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, p[(size_t)s * width]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = p[(size_t)s * width];
-        if (ms != -INFINITY) l += p[(size_t)s * width + 1] * exp2f(ms - m);
-    }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    for (int c = lane; c < rank; c += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
+// One block per (token, head) pair: the parts' weights first (their maxima and sums, in the order of the parts), then
+// every thread adds up its columns over the parts.
+#define LB_MERGE_MAX 64
+__global__ void __launch_bounds__(128) latent_attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ scratch,
+                                                                     long first_pair, int rank, int splits) {
+    __shared__ float wgt[LB_MERGE_MAX];
+    __shared__ float inv_l;
+    const long i = first_pair + blockIdx.x;
+    const int width = rank + 2;
+    const float* p = scratch + i * splits * width;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m = -INFINITY;
+        for (int s = lane; s < splits; s += 32) m = fmaxf(m, p[(size_t)s * width]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = lane; s < splits; s += 32) {
             const float ms = p[(size_t)s * width];
-            if (ms != -INFINITY) acc += p[(size_t)s * width + 2 + c] * exp2f(ms - m);
+            const float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
+            wgt[s] = w;
+            l += w * p[(size_t)s * width + 1];
         }
-        out[(first_pair + i) * rank + c] = __float2bfloat16_rn(acc * inv);
+        l = warp_sum(l);
+        if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_l;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) acc = fmaf(wgt[s], p[(size_t)s * width + 2 + c], acc);
+        out[i * rank + c] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -308,7 +318,7 @@ extern "C" int hb_latent_attention_bf16(void* out, float* scratch, const void* q
     const int dk = rank + rot;
     if (rank % 16 || rot % 16 || rank < 16 || rank > 512) HB_REFUSE("latent attention on tensor cores: rank %d and rot %d must be multiples of 16, rank 16 to 512", rank, rot);
     if (((uintptr_t)qa | (uintptr_t)cache | (uintptr_t)out) % 16) HB_REFUSE("latent attention on tensor cores: pointers must be 16-byte aligned");
-    if (splits < 1 || (splits > 1 && !scratch)) HB_REFUSE("latent attention: %d splits need scratch", splits);
+    if (splits < 1 || splits > LB_MERGE_MAX || (splits > 1 && !scratch)) HB_REFUSE("latent attention: %d splits (1 to %d; more than one need scratch)", splits, LB_MERGE_MAX);
     cudaStream_t s = (cudaStream_t)stream;
     const int r = rank <= 128 ? 1 : rank <= 256 ? 2 : 4;
     const int warps = tokens > row1 - row0 ? 8 : 4;                     // (rows of several tokens: the larger tile)
@@ -328,8 +338,7 @@ extern "C" int hb_latent_attention_bf16(void* out, float* scratch, const void* q
 #undef LB_GO
     HB_LAUNCH_CHECK("latent_attention_bf16");
     if (splits > 1) {
-        latent_attention_merge_kernel<<<(unsigned)((pairs + 3) / 4), 128, 0, s>>>((bf16*)out, scratch, (long)first_token * heads,
-                                                                                   pairs, rank, splits);
+        latent_attention_merge_kernel<<<(unsigned)pairs, 128, 0, s>>>((bf16*)out, scratch, (long)first_token * heads, rank, splits);
         HB_LAUNCH_CHECK("latent_attention_merge");
     }
     return 0;

@@ -838,13 +838,13 @@ class CudaKernels:
 
     def latent_splits(self, rows: int, heads: int, rank: int, max_kv: int) -> int:
         """Parts the keys of one-token rows are cut into for the latent attention kernel: enough that two CTAs an SM
-        have work, each part at least two tiles of 64 keys, at most 32. A function of the batch's size and the longest
+        have work, each part at least one tile of 64 keys, at most 32. A function of the batch's size and the longest
         row only (under a CUDA graph: of the bucket its plan pinned)."""
         if self.latent_split:                                            # (tests: a fixed number of parts)
             return int(self.latent_split)
         tile = 64 if rank <= 128 else 32 if rank <= 256 else 16          # (token, head) pairs a CTA of four warps
         ctas = rows * (-(-heads // tile))
-        return max(1, min(32, -(-max_kv // 64) // 2, (2 * self.sms) // max(1, ctas)))
+        return max(1, min(32, -(-max_kv // 64), (2 * self.sms) // max(1, ctas)))
 
     def sigmoid_gate(self, o, g) -> None:
         """o [tokens, n] *= sigmoid(g [tokens, n]); g may be a view into wider rows."""
@@ -866,6 +866,20 @@ class CudaKernels:
                               "counts int32 [2 experts + 1]")
         self._call("hb_route_top", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"), self._p(z),
                    z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)))
+
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize) -> None:
+        """`route_top` and `expert_rows` as one call (one launch for a few tokens). counts int32 [2 experts + 3] need not
+        be zeroed; afterwards counts[2 experts + 1:] = (0, tokens)."""
+        self._check(chosen, weight, counts, place, token_of, z)
+        t, top = chosen.shape
+        if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
+                or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 3 or place.shape[0] != t * top \
+                or token_of.shape[0] != t * top:
+            raise KernelError("route_rows: z float32 [tokens, >= experts], chosen int32 and weight float32 [tokens, top], "
+                              "counts int32 [2 experts + 3], place and token_of int32 [tokens * top]")
+        self._call("hb_route_rows", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"),
+                   self._i32(place, "place"), self._i32(token_of, "token_of"), self._p(z), z.shape[1], t, int(experts), top,
+                   ctypes.c_float(scale), int(bool(renormalize)))
 
     def expert_rows(self, place, token_of, counts, chosen, experts) -> None:
         self._check(place, token_of, counts, chosen)

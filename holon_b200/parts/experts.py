@@ -5,9 +5,11 @@
     y = Σ_chosen weight_e · W_down,e act(W_up,e x)  +  sigmoid(w_sg · x) · W_down,s act(W_up,s x)   (the shared expert, if any)
 
 `activation`: "relu2" (the square of relu) or "silu". The tokens are not sorted on the host: the router's kernel
-counts the tokens of each expert, a scan lays the (token, choice) pairs out expert by expert, the two products run
-over those rows tile by tile (every tile of one expert's weight), and a last kernel adds each token's `top` rows in
-the order of its choices, so the sum does not depend on what else is in the batch.
+counts the tokens of each expert and lays the (token, choice) pairs out expert by expert (one launch for the few
+tokens of a decode step), the two products run over those rows tile by tile (every tile of one expert's weight), and
+a last kernel adds each token's `top` rows in the order of its choices, so the sum does not depend on what else is in
+the batch. For few tokens the shared expert's first product runs in the experts' kernel too, as one expert that
+takes every token, with its activation in the epilogue.
 
 The experts' weights are stacked: up [experts · inter, hidden], down [experts · hidden, inter]; the router's rows
 and the shared expert's gate row are one product with 32-bit output.
@@ -54,25 +56,31 @@ class Experts(Part):
                     name = prefix + name[len(prefix + child):]
             yield name, p, rows
 
+    FEW = 64                 # rows up to which the shared expert's first product runs in the experts' kernel
+
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         t, k, ctx, e, top = x.shape[0], self.ctx.kernels, self.ctx, self.experts, self.top
         z = self.router.forward(x, out_dtype=torch.float32)             # [t, experts (+ 1)]: router logits, gate
         chosen = ctx.empty(t, top, dtype=torch.int32)
         weight = ctx.empty(t, top, dtype=torch.float32)
-        counts = torch.zeros(2 * e + 1, dtype=torch.int32, device=ctx.device)   # per expert: tokens, then first row (+ end)
-        k.route_top(chosen, weight, counts, z, e, self.scale, self.renormalize)
+        counts = ctx.empty(2 * e + 3, dtype=torch.int32)                 # per expert: tokens, then first row; end; (0, t)
         place = ctx.empty(t * top, dtype=torch.int32)                    # the row of each (token, choice)
         token_of = ctx.empty(t * top, dtype=torch.int32)                 # the token of each row
-        k.expert_rows(place, token_of, counts, chosen, e)
-        starts = counts[e:]
+        k.route_rows(chosen, weight, counts, place, token_of, z, e, self.scale, self.renormalize)
+        starts = counts[e:2 * e + 1]
         act = ctx.empty(t * top, self.inter)
         k.expert_linear(act, x, token_of, self.up.tensor.view(e, self.inter, self.hidden), starts, self.act)
         y = ctx.empty(t * top, self.hidden)
         k.expert_linear(y, act, None, self.down.tensor.view(e, self.hidden, self.inter), starts, 0)
         shared = None
         if self.shared_up is not None:
-            hs = self.shared_up.forward(x)
-            k.activation(hs, self.act)
+            if t <= self.FEW:                                            # few rows: the activation in the product's epilogue
+                hs = ctx.empty(t, self.shared_inter)
+                k.expert_linear(hs, x, None, self.shared_up.weight.tensor.view(1, self.shared_inter, self.hidden),
+                                counts[2 * e + 1:], self.act)
+            else:
+                hs = self.shared_up.forward(x)
+                k.activation(hs, self.act)
             shared = self.shared_down.forward(hs)
         out = ctx.empty(t, self.hidden)
         k.expert_combine(out, y, place, weight, shared, z if shared is not None else None, e)

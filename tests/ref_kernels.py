@@ -227,12 +227,18 @@ class RefKernels:
         weight.copy_(w * scale)
         counts[:experts] += torch.bincount(order.reshape(-1), minlength=experts).to(torch.int32)
 
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize):
+        counts.zero_()
+        self.route_top(chosen, weight, counts, z, experts, scale, renormalize)
+        self.expert_rows(place, token_of, counts, chosen, experts)
+        counts[2 * experts + 1], counts[2 * experts + 2] = 0, chosen.shape[0]
+
     def expert_rows(self, place, token_of, counts, chosen, experts):
         """counts[experts:] = first row of each expert and the end; pairs laid out expert by expert."""
         t, top = chosen.shape
         starts = torch.zeros(experts + 1, dtype=torch.int64)
         starts[1:] = torch.cumsum(counts[:experts].long(), 0)
-        counts[experts:] = starts.to(torch.int32)
+        counts[experts:2 * experts + 1] = starts.to(torch.int32)
         order = torch.argsort(chosen.reshape(-1).long(), stable=True)
         place[order] = torch.arange(t * top, dtype=torch.int32)
         token_of.copy_((order // top).to(torch.int32))

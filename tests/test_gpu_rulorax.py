@@ -212,6 +212,27 @@ def test_route_top(K, experts, top):
             assert torch.allclose(weight.cpu().double().sort(-1).values, s.sort(-1).values, rtol=1e-5)
 
 
+@pytest.mark.parametrize("experts,top,tokens", [(16, 4, 8), (5, 5, 64), (1, 1, 3), (300, 8, 33), (9, 2, 300), (1100, 3, 20)])
+def test_route_rows_in_one_call(K, experts, top, tokens):
+    """Few tokens take one launch, many (or more than 1,024 experts) the separate kernels: the same choices, counts and
+    first rows as the twin, every pair a row of its own in its expert's stretch, and the (0, tokens) pair behind them."""
+    z = rand(tokens, experts + 1, seed=4, scale=2.0)
+    chosen, weight = torch.empty(tokens, top, dtype=torch.int32, device=DEV), torch.empty(tokens, top, device=DEV)
+    counts = torch.full((2 * experts + 3,), -7, dtype=torch.int32, device=DEV)
+    place, token_of = (torch.empty(tokens * top, dtype=torch.int32, device=DEV) for _ in range(2))
+    K.route_rows(chosen, weight, counts, place, token_of, z.to(DEV), experts, 0.6, True)
+    c_w, w_w, n_w = torch.empty(tokens, top, dtype=torch.int32), torch.empty(tokens, top), torch.empty(2 * experts + 3, dtype=torch.int32)
+    p_w, t_w = (torch.empty(tokens * top, dtype=torch.int32) for _ in range(2))
+    REF.route_rows(c_w, w_w, n_w, p_w, t_w, z, experts, 0.6, True)
+    assert torch.equal(chosen.cpu(), c_w) and torch.equal(counts.cpu(), n_w)
+    assert torch.allclose(weight.cpu(), w_w, rtol=1e-5, atol=1e-7)
+    place, token_of, starts = place.cpu().long(), token_of.cpu().long(), counts.cpu()[experts:2 * experts + 1].long()
+    assert sorted(place.tolist()) == list(range(tokens * top))
+    assert torch.equal(token_of[place], torch.arange(tokens * top) // top)
+    e = c_w.long().reshape(-1)
+    assert bool(((place >= starts[e]) & (place < starts[e + 1])).all())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tile_rows", [0, 16, 64])
 @pytest.mark.parametrize("experts,top,tokens,hidden,inter,act", [(6, 2, 50, 72, 40, 1), (16, 4, 3, 64, 96, 1), (3, 3, 130, 40, 20, 2),

@@ -407,10 +407,11 @@ extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int3
 
 // ---------------------------------------------------------------- the experts' products in bfloat16 on tensor cores
 // The same tiles (expert by expert, at most ceil(rows / BM) + experts of them), mma.sync m16n8k16 with 32-bit sums:
-// BM x 128 outputs a CTA of four warps, the k range in steps of 32 through a three-stage cp.async ring. x rows are
+// BM x 128 outputs a CTA (four warps; eight for BM = 128), the k range in steps of 32 through a three-stage cp.async ring. x rows are
 // gathered by token_of while they are copied (rows past the expert's end are zero-filled), the weight tile is 128 rows
-// of w[e]. BM = 64 for prompts (many rows an expert), 16 for decode steps (a row or two an expert: the weight streams
-// once either way, and a 16-row tile wastes a quarter of the tensor work a 64-row tile would). k and n multiples of 8.
+// of w[e]. BM = 128 or 64 for prompts (hundreds or dozens of rows an expert), 16 for decode steps (a row or two an
+// expert: the weight streams once either way, and a 16-row tile wastes a quarter of the tensor work a 64-row tile
+// would). k and n multiples of 8.
 #define XB_BN 128
 #define XB_BK 32
 #define XB_LD (XB_BK + 8)
@@ -432,16 +433,18 @@ __device__ __forceinline__ void xb_mma(float (&c)[4], const uint32_t (&a)[4], ui
 }
 
 template <int BM>
-__global__ void __launch_bounds__(128) expert_linear_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ x,
+__global__ void __launch_bounds__(BM == 128 ? 256 : 128) expert_linear_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ x,
                                                                  const int32_t* __restrict__ token_of,
                                                                  const bf16* __restrict__ w,
                                                                  const int32_t* __restrict__ starts, int experts, int n,
                                                                  int k, int act) {
-    constexpr int WARPS_M = BM == 64 ? 2 : 1, WARPS_N = 4 / WARPS_M;
+    constexpr int WARPS = BM == 128 ? 8 : 4, THREADS = WARPS * 32;
+    constexpr int WARPS_M = BM == 128 ? 4 : BM == 64 ? 2 : 1, WARPS_N = WARPS / WARPS_M;
     constexpr int MF = BM / 16 / WARPS_M;                       // 16-row fragments a warp
     constexpr int NF = XB_BN / 8 / WARPS_N;                     // 8-column fragments a warp
-    __shared__ __align__(16) bf16 as[XB_STAGES][BM][XB_LD];
-    __shared__ __align__(16) bf16 bs[XB_STAGES][XB_BN][XB_LD];
+    extern __shared__ __align__(16) unsigned char xb_smem[];
+    bf16 (*as)[BM][XB_LD] = (bf16 (*)[BM][XB_LD])xb_smem;                                              // [stages][BM][ld]
+    bf16 (*bs)[XB_BN][XB_LD] = (bf16 (*)[XB_BN][XB_LD])(xb_smem + sizeof(bf16) * XB_STAGES * BM * XB_LD);   // [stages][128][ld]
     __shared__ int src[BM];
     __shared__ int tile_info[3];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -461,7 +464,7 @@ __global__ void __launch_bounds__(128) expert_linear_bf16_kernel(bf16* __restric
 
     auto load = [&](int kt, int stage) {
         const int k0 = kt * XB_BK;
-        for (int c = tid; c < (BM + XB_BN) * 4; c += 128) {      // 16-byte pieces: four a row
+        for (int c = tid; c < (BM + XB_BN) * 4; c += THREADS) {  // 16-byte pieces: four a row
             const int r = c >> 2, col = (c & 3) * 8;
             const bool in_k = k0 + col < k;
             if (r < BM) {
@@ -530,25 +533,26 @@ __global__ void __launch_bounds__(128) expert_linear_bf16_kernel(bf16* __restric
     }
 }
 
-// tile_rows: 16 or 64 rows a tile (0: chosen from the rows an expert gets on average).
+// tile_rows: 16, 64 or 128 rows a tile (0: chosen from the rows an expert gets on average).
 extern "C" int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w,
                                      const int32_t* starts, int rows, int experts, int n, int k, int act, int tile_rows,
                                      hb_stream stream) {
     if (rows == 0 || n == 0) return 0;
     if (k <= 0 || k % 8 || n % 8 || experts < 1) HB_REFUSE("expert_linear_bf16: k = %d and n = %d must be multiples of 8", k, n);
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) HB_REFUSE("expert_linear_bf16: pointers must be 16-byte aligned");
-    const int bm = tile_rows ? tile_rows : (rows <= 8 * experts ? 16 : 64);
-    if (bm != 16 && bm != 64) HB_REFUSE("expert_linear_bf16: tiles of %d rows; 16 or 64", bm);
+    const int bm = tile_rows ? tile_rows : (rows <= 8 * experts ? 16 : rows <= 96 * experts ? 64 : 128);
+    if (bm != 16 && bm != 64 && bm != 128) HB_REFUSE("expert_linear_bf16: tiles of %d rows; 16, 64 or 128", bm);
     const long tiles = (rows + bm - 1) / bm + experts;
     if (tiles > 65535) HB_REFUSE("expert_linear_bf16: %d rows over %d experts are above the kernel's limit", rows, experts);
     dim3 grid((n + XB_BN - 1) / XB_BN, (unsigned)tiles);
     cudaStream_t s = (cudaStream_t)stream;
-    if (bm == 16)
-        expert_linear_bf16_kernel<16><<<grid, 128, 0, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts,
-                                                           experts, n, k, act);
-    else
-        expert_linear_bf16_kernel<64><<<grid, 128, 0, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts,
-                                                           experts, n, k, act);
+    const size_t smem = sizeof(bf16) * XB_STAGES * (size_t)(bm + XB_BN) * XB_LD;
+#define XB_GO(BM_, T_) do { \
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(expert_linear_bf16_kernel<BM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        expert_linear_bf16_kernel<BM_><<<grid, T_, smem, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts, experts, n, k, act); \
+    } while (0)
+    if (bm == 16) XB_GO(16, 128); else if (bm == 64) XB_GO(64, 128); else XB_GO(128, 256);
+#undef XB_GO
     HB_LAUNCH_CHECK("expert_linear_bf16");
     return 0;
 }

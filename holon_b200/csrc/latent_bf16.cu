@@ -140,7 +140,33 @@ __global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
 #pragma unroll
             for (int i = 0; i < 2 * NP; ++i) { sp[i][0] = sp[i][1] = sp[i][2] = sp[i][3] = 0.f; }
             const int key0 = part * NP * 16;
-            for (int kk = 0; kk < dk; kk += 16) {
+            int kk = 0;
+            if constexpr (NP <= 2) {
+                // few cache rows a warp: two sets of sums over alternate steps of 16, so that a product does not wait
+                // for the one before it (the sets are added below)
+                float sq[2 * NP][4];
+#pragma unroll
+                for (int i = 0; i < 2 * NP; ++i) { sq[i][0] = sq[i][1] = sq[i][2] = sq[i][3] = 0.f; }
+                for (; kk + 32 <= dk; kk += 32) {
+                    uint32_t a0[4], a1[4];
+                    lb_ldsm4(a0, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
+                    lb_ldsm4(a1, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        uint32_t b0[4], b1[4];
+                        const bf16* kr = kt_s + (size_t)(key0 + q * 16 + (lane & 7) + (lane >> 4) * 8) * ld + kk + ((lane >> 3) & 1) * 8;
+                        lb_ldsm4(b0, kr);
+                        lb_ldsm4(b1, kr + 16);
+                        lb_mma(sp[2 * q], a0, b0[0], b0[1]);
+                        lb_mma(sq[2 * q], a1, b1[0], b1[1]);
+                        lb_mma(sp[2 * q + 1], a0, b0[2], b0[3]);
+                        lb_mma(sq[2 * q + 1], a1, b1[2], b1[3]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 2 * NP; ++i) { sp[i][0] += sq[i][0]; sp[i][1] += sq[i][1]; sp[i][2] += sq[i][2]; sp[i][3] += sq[i][3]; }
+            }
+            for (; kk < dk; kk += 16) {
                 uint32_t a[4];
                 lb_ldsm4(a, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
 #pragma unroll

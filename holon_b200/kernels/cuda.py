@@ -128,7 +128,7 @@ class CudaKernels:
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.latent_split = None              # tests: a fixed number of key parts for one-token rows of latent attention
         self.expert_products = "fast"         # "generic" forces the CUDA-core kernel for bfloat16 experts too (tests)
-        self.expert_tile_rows = 0             # tests: 16 or 64 rows a tile of the experts' tensor-core products (0: chosen)
+        self.expert_tile_rows = 0             # tests: 16, 64 or 128 rows a tile of the experts' tensor-core products (0: chosen)
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
         # Decode steps: the products of a layer that follow one another on the same few rows (the mixer's last, the
         # feed-forward's two, the next mixer's first) can be queued and run in one launch; every other call of this table

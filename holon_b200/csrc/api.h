@@ -160,7 +160,7 @@ int hb_expert_linear(void* out, const void* x, int dtype, const int32_t* token_o
                      int rows, int experts, int n, int k, int act, hb_stream stream);
 int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight, const void* shared,
                       const float* z, int ldz, int gate_at, int tokens, int top, int hidden, hb_stream stream);
-// hb_expert_linear in bfloat16 on tensor cores: k and n multiples of 8; tile_rows 16, 64 or 128 rows a tile (0: chosen
+// hb_expert_linear in bfloat16 on tensor cores: k and n multiples of 8; tile_rows 8 (on CUDA cores, for a row or two an expert), 16, 64 or 128 rows a tile (0: chosen
 // from the rows an expert gets on average).
 int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w, const int32_t* starts, int rows,
                           int experts, int n, int k, int act, int tile_rows, hb_stream stream);

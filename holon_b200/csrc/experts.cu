@@ -238,16 +238,34 @@ __device__ __forceinline__ float expert_act(float v, int act) {
 #define EBN 64
 #define EBK 16
 
-// Finds the expert and the first row of m-tile `tile` (tiles of EBM rows, counted expert by expert); false: no such tile.
-__device__ __forceinline__ bool expert_tile(const int32_t* __restrict__ starts, int experts, int tile, int bm, int& e_out,
-                                            int& row0, int& row_end) {
-    for (int e = 0; e < experts; ++e) {
-        const int a = starts[e], b = starts[e + 1];
-        const int tiles = (b - a + bm - 1) / bm;
-        if (tile < tiles) { e_out = e; row0 = a + tile * bm; row_end = b; return true; }
-        tile -= tiles;
+// Finds the expert and the first row of m-tile `tile` (tiles of `bm` rows, counted expert by expert). Called by every
+// thread of the block; the first warp reads the experts' first rows 32 at a time and adds up their tile counts with
+// shuffles; info[0] = the expert (-1: no such tile), info[1] = the tile's first row, info[2] = the expert's end.
+__device__ __forceinline__ void expert_tile(const int32_t* __restrict__ starts, int experts, int tile, int bm, int* info) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int base = 0, found = -1, row0 = 0, row_end = 0;
+        for (int e0 = 0; e0 < experts && found < 0; e0 += 32) {
+            const int e = e0 + lane;
+            const int a = e < experts ? starts[e] : 0, b = e < experts ? starts[e + 1] : 0;
+            const int tiles = (b - a + bm - 1) / bm;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+            const int before = base + incl - tiles;
+            const bool hit = tile >= before && tile < before + tiles;
+            const unsigned who = __ballot_sync(0xffffffffu, hit);
+            if (who) {
+                const int src = __ffs(who) - 1;
+                found = e0 + src;
+                row0 = __shfl_sync(0xffffffffu, a, src) + (tile - __shfl_sync(0xffffffffu, before, src)) * bm;
+                row_end = __shfl_sync(0xffffffffu, b, src);
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) { info[0] = found; info[1] = row0; info[2] = row_end; }
     }
-    return false;
+    __syncthreads();
 }
 
 template <typename T>
@@ -259,12 +277,7 @@ __global__ void __launch_bounds__(256) expert_linear_kernel(T* __restrict__ out,
     __shared__ float ws[EBK][EBN + 4];
     __shared__ int src[EBM];
     __shared__ int tile_info[3];
-    if (threadIdx.x == 0) {
-        int e = 0, r0 = 0, r1 = 0;
-        const bool ok = expert_tile(starts, experts, blockIdx.y, EBM, e, r0, r1);
-        tile_info[0] = ok ? e : -1; tile_info[1] = r0; tile_info[2] = r1;
-    }
-    __syncthreads();
+    expert_tile(starts, experts, blockIdx.y, EBM, tile_info);
     const int e = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
     if (e < 0) return;
     const int tid = threadIdx.x;
@@ -312,7 +325,8 @@ extern "C" int hb_expert_linear(void* out, const void* x, int dtype, const int32
                                 const int32_t* starts, int rows, int experts, int n, int k, int act, hb_stream stream) {
     if (rows == 0 || n == 0) return 0;
     if (k <= 0 || experts < 1) HB_REFUSE("expert_linear: k = %d, %d experts", k, experts);
-    const long tiles = (rows + EBM - 1) / EBM + experts;          // the most m-tiles any split of the rows can have
+    const long tiles = (rows + EBM - 1) / EBM + (experts < rows ? experts : rows);   // the most m-tiles any split of the rows can have:
+                                                                                      // an expert with rows adds at most one partial tile
     if (tiles > 65535) HB_REFUSE("expert_linear: %d rows over %d experts are above the kernel's limit", rows, experts);
     dim3 grid((n + EBN - 1) / EBN, (unsigned)tiles);
     cudaStream_t s = (cudaStream_t)stream;
@@ -376,7 +390,7 @@ __global__ void expert_combine_kernel(T* __restrict__ out, const T* __restrict__
     if (kept && threadIdx.x < top) { rows[threadIdx.x] = place[t * top + threadIdx.x]; wgt[threadIdx.x] = weight[t * top + threadIdx.x]; }
     __syncthreads();
     const float gate = shared ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const int p = kept ? rows[k] : place[t * top + k];
@@ -392,13 +406,14 @@ extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int3
                                  hb_stream stream) {
     if (tokens == 0) return 0;
     if (shared && (!z || gate_at >= ldz)) HB_REFUSE("expert_combine: a shared expert needs its gate's logit");
-    const int threads = hidden >= 2048 ? 512 : hidden >= 1024 ? 256 : 128;
+    const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(tokens, tokens >= 1024 ? 1 : (hidden + threads - 1) / threads);     // few tokens: a block every `threads` columns
     if (dtype == HB_F32)
-        expert_combine_kernel<float><<<tokens, threads, 0, s>>>((float*)out, (const float*)y, place, weight,
+        expert_combine_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)y, place, weight,
                                                                 (const float*)shared, z, ldz, gate_at, top, hidden);
     else if (dtype == HB_BF16)
-        expert_combine_kernel<bf16><<<tokens, threads, 0, s>>>((bf16*)out, (const bf16*)y, place, weight,
+        expert_combine_kernel<bf16><<<grid, threads, 0, s>>>((bf16*)out, (const bf16*)y, place, weight,
                                                                (const bf16*)shared, z, ldz, gate_at, top, hidden);
     else HB_REFUSE("expert_combine: dtype %d", dtype);
     HB_LAUNCH_CHECK("expert_combine");
@@ -448,12 +463,7 @@ __global__ void __launch_bounds__(BM == 128 ? 256 : 128) expert_linear_bf16_kern
     __shared__ int src[BM];
     __shared__ int tile_info[3];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) {
-        int e = 0, r0 = 0, r1 = 0;
-        const bool ok = expert_tile(starts, experts, blockIdx.y, BM, e, r0, r1);
-        tile_info[0] = ok ? e : -1; tile_info[1] = r0; tile_info[2] = r1;
-    }
-    __syncthreads();
+    expert_tile(starts, experts, blockIdx.y, BM, tile_info);
     const int e = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
     if (e < 0) return;
     if (tid < BM) src[tid] = m0 + tid < m_end ? (token_of ? token_of[m0 + tid] : m0 + tid) : -1;
@@ -533,19 +543,105 @@ __global__ void __launch_bounds__(BM == 128 ? 256 : 128) expert_linear_bf16_kern
     }
 }
 
-// tile_rows: 16, 64 or 128 rows a tile (0: chosen from the rows an expert gets on average).
+// ---------------------------------------------------------------- a row or two an expert (decode steps)
+// Tiles of 8 rows; the product is bound by reading each chosen expert's weight once, and what counts is how many bytes
+// are on their way: a CTA of eight warps keeps the tile's rows of x in shared memory and takes 32 weight rows, four a
+// warp; a lane reads 16 bytes of each of them per step of 256 columns (two steps in flight) and multiplies on the CUDA
+// cores in 32-bit; the lanes' sums meet by shuffles. No tensor cores: with one or two rows they would idle anyway.
+#define XF_ROWS 8
+#define XF_WROWS 4
+
+__global__ void __launch_bounds__(256) expert_linear_few_kernel(bf16* __restrict__ out, const bf16* __restrict__ x,
+                                                                const int32_t* __restrict__ token_of,
+                                                                const bf16* __restrict__ w,
+                                                                const int32_t* __restrict__ starts, int experts, int n,
+                                                                int k, int act) {
+    extern __shared__ __align__(16) unsigned char xf_smem[];
+    bf16* xs = (bf16*)xf_smem;                              // [XF_ROWS][k]
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    expert_tile(starts, experts, blockIdx.y, XF_ROWS, tile_info);
+    const int e = tile_info[0], m0 = tile_info[1];
+    if (e < 0) return;
+    const int nrows = min(XF_ROWS, tile_info[2] - m0);
+    const int chunks = k >> 3;
+    for (int c = tid; c < nrows * chunks; c += 256) {
+        const int r = c / chunks, col = (c % chunks) * 8;
+        const int src = token_of ? token_of[m0 + r] : m0 + r;
+        *(uint4*)(xs + (size_t)r * k + col) = __ldg((const uint4*)(x + (size_t)src * k + col));
+    }
+    __syncthreads();
+    const int nr = blockIdx.x * 32 + warp * XF_WROWS;       // this warp's first weight row
+    if (nr >= n) return;
+    const bf16* we = w + (size_t)e * n * k;
+    float acc[XF_WROWS][XF_ROWS];
+#pragma unroll
+    for (int j = 0; j < XF_WROWS; ++j)
+#pragma unroll
+        for (int r = 0; r < XF_ROWS; ++r) acc[j][r] = 0.f;
+#pragma unroll 2
+    for (int kc = lane * 8; kc < k; kc += 256) {
+        uint4 wv[XF_WROWS];
+#pragma unroll
+        for (int j = 0; j < XF_WROWS; ++j)
+            wv[j] = nr + j < n ? __ldg((const uint4*)(we + (size_t)(nr + j) * k + kc)) : make_uint4(0u, 0u, 0u, 0u);
+        float wf[XF_WROWS][8];
+#pragma unroll
+        for (int j = 0; j < XF_WROWS; ++j) {
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&wv[j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); wf[j][2 * i] = f.x; wf[j][2 * i + 1] = f.y; }
+        }
+#pragma unroll
+        for (int r = 0; r < XF_ROWS; ++r) {
+            if (r < nrows) {
+                const uint4 xv = *(const uint4*)(xs + (size_t)r * k + kc);
+                const __nv_bfloat162* h = (const __nv_bfloat162*)&xv;
+                float xf[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); xf[2 * i] = f.x; xf[2 * i + 1] = f.y; }
+#pragma unroll
+                for (int j = 0; j < XF_WROWS; ++j)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j][r] = fmaf(wf[j][i], xf[i], acc[j][r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < XF_ROWS; ++r) {
+        if (r < nrows) {
+#pragma unroll
+            for (int j = 0; j < XF_WROWS; ++j) {
+                const float v = warp_sum(acc[j][r]);
+                if (lane == 0 && nr + j < n) out[(size_t)(m0 + r) * n + nr + j] = __float2bfloat16_rn(expert_act(v, act));
+            }
+        }
+    }
+}
+
+// tile_rows: 8 (the kernel above), 16, 64 or 128 rows a tile (0: chosen from the rows an expert gets on average).
 extern "C" int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w,
                                      const int32_t* starts, int rows, int experts, int n, int k, int act, int tile_rows,
                                      hb_stream stream) {
     if (rows == 0 || n == 0) return 0;
     if (k <= 0 || k % 8 || n % 8 || experts < 1) HB_REFUSE("expert_linear_bf16: k = %d and n = %d must be multiples of 8", k, n);
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) HB_REFUSE("expert_linear_bf16: pointers must be 16-byte aligned");
-    const int bm = tile_rows ? tile_rows : (rows <= 8 * experts ? 16 : rows <= 96 * experts ? 64 : 128);
-    if (bm != 16 && bm != 64 && bm != 128) HB_REFUSE("expert_linear_bf16: tiles of %d rows; 16, 64 or 128", bm);
-    const long tiles = (rows + bm - 1) / bm + experts;
+    const bool fits = (size_t)XF_ROWS * k * sizeof(bf16) <= 200 * 1024;
+    const int bm = tile_rows ? tile_rows : (rows <= 8 * experts && fits ? 8 : rows <= 16 * experts ? 16 : rows <= 96 * experts ? 64 : 128);
+    if (bm != 8 && bm != 16 && bm != 64 && bm != 128) HB_REFUSE("expert_linear_bf16: tiles of %d rows; 8, 16, 64 or 128", bm);
+    if (bm == 8 && !fits) HB_REFUSE("expert_linear_bf16: rows of %d columns do not fit the 8-row kernel's shared memory", k);
+    const long tiles = (rows + bm - 1) / bm + (experts < rows ? experts : rows);
     if (tiles > 65535) HB_REFUSE("expert_linear_bf16: %d rows over %d experts are above the kernel's limit", rows, experts);
     dim3 grid((n + XB_BN - 1) / XB_BN, (unsigned)tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (bm == 8) {
+        const size_t smem = (size_t)XF_ROWS * k * sizeof(bf16);
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(expert_linear_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 few((n + 31) / 32, (unsigned)tiles);
+        expert_linear_few_kernel<<<few, 256, smem, s>>>((bf16*)out, (const bf16*)x, token_of, (const bf16*)w, starts, experts, n, k, act);
+        HB_LAUNCH_CHECK("expert_linear_few");
+        return 0;
+    }
     const size_t smem = sizeof(bf16) * XB_STAGES * (size_t)(bm + XB_BN) * XB_LD;
 #define XB_GO(BM_, T_) do { \
         if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(expert_linear_bf16_kernel<BM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \

@@ -24,17 +24,19 @@ __global__ void latent_prepare_kernel(T* __restrict__ qa, const T* __restrict__ 
     const bool turn = half > 0 && p >= 0 && p < max_positions;
     const float* cs = table + (size_t)(turn ? p : 0) * rot_dims;           // cosines, then sines
     const int dk = rank + rot;
-    // each head's rotated query part -> qa[t, h, rank:]
-    for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
-        const int h = i / rot, d = i % rot;
+    if ((int)blockIdx.y < heads) {                     // this head's rotated query part -> qa[t, h, rank:]
+        const int h = blockIdx.y;
         const T* q = fr + (size_t)h * (dim + rot) + dim;
-        float v = to_f32(q[d]);
-        if (turn && d < rot_dims) {
-            const int j = d < half ? d : d - half;
-            const float c = cs[j], s = cs[half + j];
-            v = d < half ? v * c - to_f32(q[d + half]) * s : v * c + to_f32(q[d - half]) * s;
+        for (int d = threadIdx.x; d < rot; d += blockDim.x) {
+            float v = to_f32(q[d]);
+            if (turn && d < rot_dims) {
+                const int j = d < half ? d : d - half;
+                const float c = cs[j], s = cs[half + j];
+                v = d < half ? v * c - to_f32(q[d + half]) * s : v * c + to_f32(q[d - half]) * s;
+            }
+            qa[((size_t)t * heads + h) * dk + rank + d] = from_f32<T>(v);
         }
-        qa[((size_t)t * heads + h) * dk + rank + d] = from_f32<T>(v);
+        return;
     }
     if (dkv_at < 0) return;
     const long w = write_index[t];
@@ -68,7 +70,9 @@ extern "C" int hb_latent_prepare(void* qa, const void* first, int dtype, int ld,
     if (dkv_at >= 0 && dkv_at + rank + rot > ld) HB_REFUSE("latent_prepare: the down-projection's columns end past the row");
     cudaStream_t s = (cudaStream_t)stream;
     const long cache_rows = (long)pages * page_size;
-#define LP_GO(T_, TW_) latent_prepare_kernel<T_, TW_><<<tokens, 128, 0, s>>>((T_*)qa, (const T_*)first, ld, heads, dim, rot, \
+    if (heads + 1 > 65535) HB_REFUSE("latent_prepare: %d heads", heads);
+    dim3 grid(tokens, heads + (dkv_at >= 0 ? 1 : 0));      // a block a head, and one for the token's cache row
+#define LP_GO(T_, TW_) latent_prepare_kernel<T_, TW_><<<grid, 128, 0, s>>>((T_*)qa, (const T_*)first, ld, heads, dim, rot, \
         rank, dkv_at, positions, table, rot_dims, max_positions, (const TW_*)norm_weight, eps, (T_*)cache, write_index, cache_rows)
     if (dtype == HB_F32) LP_GO(float, float);
     else if (dtype == HB_BF16 && weight_dtype == HB_F32) LP_GO(bf16, float);

@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
 // One block per (token, head) pair: the parts' weights first (their maxima and sums, in the order of the parts), then
 // every thread adds up its columns over the parts.
 #define LB_MERGE_MAX 64
-__global__ void __launch_bounds__(128) latent_attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ scratch,
+__global__ void __launch_bounds__(512) latent_attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ scratch,
                                                                      long first_pair, int rank, int splits) {
     __shared__ float wgt[LB_MERGE_MAX];
     __shared__ float inv_l;
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(128) latent_attention_merge_kernel(bf16* __res
     const float inv = inv_l;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float acc = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) acc = fmaf(wgt[s], p[(size_t)s * width + 2 + c], acc);
         out[i * rank + c] = __float2bfloat16_rn(acc * inv);
     }
@@ -364,7 +364,7 @@ extern "C" int hb_latent_attention_bf16(void* out, float* scratch, const void* q
 #undef LB_GO
     HB_LAUNCH_CHECK("latent_attention_bf16");
     if (splits > 1) {
-        latent_attention_merge_kernel<<<(unsigned)pairs, 128, 0, s>>>((bf16*)out, scratch, (long)first_token * heads, rank, splits);
+        latent_attention_merge_kernel<<<(unsigned)pairs, min(512, (rank + 31) / 32 * 32), 0, s>>>((bf16*)out, scratch, (long)first_token * heads, rank, splits);
         HB_LAUNCH_CHECK("latent_attention_merge");
     }
     return 0;

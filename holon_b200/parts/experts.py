@@ -56,7 +56,7 @@ class Experts(Part):
                     name = prefix + name[len(prefix + child):]
             yield name, p, rows
 
-    FEW = 64                 # rows up to which the shared expert's first product runs in the experts' kernel
+    FEW = 8                  # rows up to which the shared expert's first product runs in the experts' kernel
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         t, k, ctx, e, top = x.shape[0], self.ctx.kernels, self.ctx, self.experts, self.top

@@ -234,7 +234,7 @@ def test_route_rows_in_one_call(K, experts, top, tokens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tile_rows", [0, 16, 64, 128])
+@pytest.mark.parametrize("tile_rows", [0, 8, 16, 64, 128])
 @pytest.mark.parametrize("experts,top,tokens,hidden,inter,act", [(6, 2, 50, 72, 40, 1), (16, 4, 3, 64, 96, 1), (3, 3, 130, 40, 20, 2),
                                                                  (40, 1, 9, 32, 8, 0), (5, 2, 200, 328, 136, 1), (3, 1, 70, 100, 52, 1)])
 def test_expert_rows_products_and_sum(K, dtype, experts, top, tokens, hidden, inter, act, tile_rows, monkeypatch):

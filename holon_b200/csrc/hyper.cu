@@ -34,35 +34,48 @@ __global__ void hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const flo
     const bool fold = y != nullptr, write = index == nullptr && (fold || src != nullptr);
     float* xr = xs + t * (size_t)n * dim;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float old[S > 0 ? S : HC_MAX_STREAMS];
-        if (src) {
-            const float v = src[t * dim + i];
+    constexpr int NS = S > 0 ? S : HC_MAX_STREAMS;
+    constexpr int U = S > 0 && S <= 4 ? 4 : 1;              // columns a thread has in flight at once
+    for (int i0 = threadIdx.x; i0 < dim; i0 += blockDim.x * U) {
+        float old[U][NS], yv[U];
 #pragma unroll
-            for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) old[s] = v;
-        } else {
+        for (int u = 0; u < U; ++u) {                       // every load of this round first
+            const int i = i0 + u * blockDim.x;
+            if (i < dim) {
+                if (src) {
+                    const float v = src[t * dim + i];
 #pragma unroll
-            for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) old[s] = xr[(size_t)s * dim + i];
-        }
-        const float yv = fold ? to_f32(y[t * dim + i]) : 0.f;
-        float u = 0.f;
+                    for (int s = 0; s < NS; ++s) if (s < n) old[u][s] = v;
+                } else {
 #pragma unroll
-        for (int q = 0; q < (S > 0 ? S : HC_MAX_STREAMS); ++q) {
-            if (q >= n) break;
-            float v;
-            if (fold) {
-                v = 0.f;
-#pragma unroll
-                for (int s = 0; s < (S > 0 ? S : HC_MAX_STREAMS); ++s) if (s < n) v = fmaf(c.mix[s * n + q], old[s], v);
-                v = fmaf(c.out[q], yv, v);
-            } else {
-                v = old[q];
+                    for (int s = 0; s < NS; ++s) if (s < n) old[u][s] = xr[(size_t)s * dim + i];
+                }
+                yv[u] = fold ? to_f32(y[t * dim + i]) : 0.f;
             }
-            if (write) xr[(size_t)q * dim + i] = v;
-            u = fmaf(c.in[q], v, u);
         }
-        row[i] = u;
-        ss += u * u;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i >= dim) continue;
+            float acc = 0.f;
+#pragma unroll
+            for (int q = 0; q < NS; ++q) {
+                if (q >= n) break;
+                float v;
+                if (fold) {
+                    v = 0.f;
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) if (s < n) v = fmaf(c.mix[s * n + q], old[u][s], v);
+                    v = fmaf(c.out[q], yv[u], v);
+                } else {
+                    v = old[u][q];
+                }
+                if (write) xr[(size_t)q * dim + i] = v;
+                acc = fmaf(c.in[q], v, acc);
+            }
+            row[i] = acc;
+            ss += acc * acc;
+        }
     }
     const float rstd = rsqrtf(block_sum(ss, scratch) / (float)dim + eps);
     TD* o = out + (size_t)r * dim;
@@ -77,16 +90,15 @@ static int hyper_launch(void* out, float* xs, const float* src, const void* y, c
     const size_t smem = (size_t)dim * sizeof(float);
 #define HC_GO(S_) hyper_mix_norm_kernel<TD, TW, S_><<<rows, threads, smem, s>>>((TD*)out, xs, src, (const TD*)y, mix, outc, \
         inc, (const TW*)weight, eps, offset, index, dim, streams)
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaSuccess;
-        if (streams == 4) e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        else if (streams == 2) e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        else e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) HB_REFUSE("hyper_mix_norm: %d columns do not fit in shared memory", dim);
+#define HC_CASE(S_) case S_: \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(hyper_mix_norm_kernel<TD, TW, S_ % HC_MAX_STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            HB_REFUSE("hyper_mix_norm: %d columns do not fit in shared memory", dim); \
+        HC_GO(S_ % HC_MAX_STREAMS); break
+    switch (streams <= 4 || streams == 8 ? streams : HC_MAX_STREAMS) {      // (16 stands for the kernel of any number)
+        HC_CASE(1); HC_CASE(2); HC_CASE(3); HC_CASE(4); HC_CASE(8);
+        default: HC_CASE(16);
     }
-    if (streams == 4) HC_GO(4);
-    else if (streams == 2) HC_GO(2);
-    else HC_GO(0);
+#undef HC_CASE
 #undef HC_GO
     HB_LAUNCH_CHECK("hyper_mix_norm");
     return 0;

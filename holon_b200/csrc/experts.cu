@@ -406,9 +406,10 @@ extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int3
                                  hb_stream stream) {
     if (tokens == 0) return 0;
     if (shared && (!z || gate_at >= ldz)) HB_REFUSE("expert_combine: a shared expert needs its gate's logit");
+    if (hidden > 65535 * 128) HB_REFUSE("expert_combine: %d columns", hidden);
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(tokens, tokens >= 1024 ? 1 : (hidden + threads - 1) / threads);     // few tokens: a block every `threads` columns
+    dim3 grid(tokens, (hidden + threads - 1) / threads);                        // a block every `threads` columns of a token
     if (dtype == HB_F32)
         expert_combine_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)y, place, weight,
                                                                 (const float*)shared, z, ldz, gate_at, top, hidden);

@@ -39,7 +39,7 @@ __global__ void hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const flo
     for (int i0 = threadIdx.x; i0 < dim; i0 += blockDim.x * U) {
         float old[U][NS], yv[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {                       // every load of this round first
+        for (int u = 0; u < U; ++u) {                       // every load of this pass first
             const int i = i0 + u * blockDim.x;
             if (i < dim) {
                 if (src) {

@@ -164,6 +164,15 @@ int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place,
 // from the rows an expert gets on average).
 int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w, const int32_t* starts, int rows,
                           int experts, int n, int k, int act, int tile_rows, hb_stream stream);
+// The same for prompts on tcgen05 tensor cores (csrc/experts_tcgen05.cu: tiles of 128 rows x 256 columns, TMA, tensor
+// memory). token_of given: x is first gathered into `gathered` [rows, k]. table: 3 * hb_expert_linear_tcgen05_tiles(rows,
+// experts) int32 of scratch. hb_experts_tcgen05_status synchronises the device and returns (and clears) the kernel's
+// bounded-wait status word.
+int hb_expert_linear_tcgen05_tiles(int rows, int experts);
+int hb_expert_linear_tcgen05(void* out, const void* x, const int32_t* token_of, void* gathered, const void* w,
+                             const int32_t* starts, int32_t* table, int rows, int experts, int n, int k, int act,
+                             hb_stream stream);
+int hb_experts_tcgen05_status(unsigned int* status);
 // x = act(x) in place (act as above); o [tokens, n] *= sigmoid(g[t * ld + i]).
 int hb_activation(void* x, int dtype, long count, int act, hb_stream stream);
 int hb_sigmoid_gate(void* o, const void* g, int dtype, int tokens, int n, long ld, hb_stream stream);

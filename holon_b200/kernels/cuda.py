@@ -127,7 +127,11 @@ class CudaKernels:
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.latent_split = None              # tests: a fixed number of key parts for one-token rows of latent attention
-        self.expert_products = "fast"         # "generic" forces the CUDA-core kernel for bfloat16 experts too (tests)
+        # The experts' products in bfloat16: "fast" (the default: tcgen05 for prompts, mma.sync tiles or the CUDA-core
+        # kernel for fewer rows an expert), "mma" (never tcgen05), "tcgen05" (always), "generic" (the kernel of any dtype).
+        self.expert_products = os.environ.get("HOLON_B200_EXPERTS", "fast")
+        if self.expert_products not in ("fast", "mma", "tcgen05", "generic"):
+            raise KernelError(f"HOLON_B200_EXPERTS must be fast, mma, tcgen05 or generic, not {self.expert_products!r}")
         self.expert_tile_rows = 0             # tests: 16, 64 or 128 rows a tile of the experts' tensor-core products (0: chosen)
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
         # Decode steps: the products of a layer that follow one another on the same few rows (the mixer's last, the
@@ -709,7 +713,7 @@ class CudaKernels:
         up their barrier and flags are put back to zero, so that the next launch starts clean."""
         out = 0
         for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status",
-                     "hb_gemm_chain_status", "hb_gemm_tickets_status", "hb_gemm_mid_status"):
+                     "hb_gemm_chain_status", "hb_gemm_tickets_status", "hb_gemm_mid_status", "hb_experts_tcgen05_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())
@@ -889,6 +893,8 @@ class CudaKernels:
         self._call("hb_expert_rows", self._i32(place, "place"), self._i32(token_of, "token_of"), self._i32(counts, "counts"),
                    self._i32(chosen, "chosen"), t, top, int(experts))
 
+    EXPERT_TCGEN05_ROWS = 96                  # rows an expert on average from which its products run on tcgen05
+
     def expert_linear(self, out, x, token_of, w, starts, act: int) -> None:
         self._check(out, x, token_of, w, starts)
         e, n, k = w.shape
@@ -896,8 +902,17 @@ class CudaKernels:
         if out.shape != (rows, n) or x.shape[1] != k or not (out.dtype == x.dtype == w.dtype) or starts.shape[0] != e + 1 \
                 or (token_of is None and x.shape[0] != rows) or (token_of is not None and token_of.shape[0] != rows):
             raise KernelError("expert_linear: x [*, k], w [experts, n, k], out [rows, n], starts int32 [experts + 1]")
-        if x.dtype == torch.bfloat16 and k % 8 == 0 and n % 8 == 0 and self.expert_products == "fast" \
-                and (x.data_ptr() | w.data_ptr() | out.data_ptr()) % 16 == 0:
+        aligned = k % 8 == 0 and n % 8 == 0 and (x.data_ptr() | w.data_ptr() | out.data_ptr()) % 16 == 0
+        if x.dtype == torch.bfloat16 and aligned and (self.expert_products == "tcgen05" or (
+                self.expert_products == "fast" and self.expert_tile_rows == 0 and rows >= self.EXPERT_TCGEN05_ROWS * e)):
+            # prompts (a hundred rows an expert and more): the tcgen05 kernel, x gathered expert by expert first
+            tiles = -(-rows // 128) + min(e, rows)
+            table = torch.empty(3 * tiles, dtype=torch.int32, device=self.device)
+            gathered = torch.empty((rows, k), dtype=x.dtype, device=self.device) if token_of is not None else None
+            return self._call("hb_expert_linear_tcgen05", self._p(out), self._p(x), self._i32(token_of, "token_of"),
+                              self._p(gathered), self._p(w), self._i32(starts, "starts"), self._i32(table, "table"), rows, e, n, k,
+                              int(act))
+        if x.dtype == torch.bfloat16 and aligned and self.expert_products in ("fast", "mma"):
             return self._call("hb_expert_linear_bf16", self._p(out), self._p(x), self._i32(token_of, "token_of"), self._p(w),
                               self._i32(starts, "starts"), rows, e, n, k, int(act), int(self.expert_tile_rows))
         self._call("hb_expert_linear", self._p(out), self._p(x), _code(x), self._i32(token_of, "token_of"), self._p(w),

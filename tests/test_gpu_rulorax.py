@@ -284,6 +284,28 @@ def test_expert_rows_products_and_sum(K, dtype, experts, top, tokens, hidden, in
         close(out, ref, dtype, scale=8.0 if dtype == torch.float32 else 16.0)
 
 
+@pytest.mark.parametrize("experts,rows,n,k,act,gather", [(4, 700, 264, 136, 1, True), (3, 130, 512, 64, 0, False), (6, 40, 72, 328, 2, True),
+                                                         (2, 1, 8, 8, 1, True), (9, 2000, 1408, 256, 1, False)])
+def test_expert_products_on_tcgen05(K, experts, rows, n, k, act, gather, monkeypatch):
+    """The prompt kernel at sizes that leave partial tiles everywhere: experts of 0 to hundreds of rows, widths that
+    end inside a 256-column tile and inside a 64-wide k block, gathered rows and rows already in order."""
+    monkeypatch.setattr(K, "expert_products", "tcgen05")
+    g = torch.Generator().manual_seed(rows)
+    cuts = torch.sort(torch.randint(0, rows + 1, (experts - 1,), generator=g)).values.tolist()
+    if experts > 2:
+        cuts[1] = cuts[0]                                                    # an expert without rows
+    starts = torch.tensor([0, *cuts, rows], dtype=torch.int32)
+    tokens = max(1, rows // 2)
+    x = rand(tokens if gather else rows, k, dtype=torch.bfloat16, seed=1)
+    token_of = torch.randint(0, tokens, (rows,), generator=g).to(torch.int32) if gather else None
+    w = rand(experts, n, k, dtype=torch.bfloat16, seed=2, scale=k ** -0.5)
+    out, want = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device=DEV), torch.empty(rows, n, dtype=torch.bfloat16)
+    K.expert_linear(out, x.to(DEV), token_of.to(DEV) if gather else None, w.to(DEV), starts.to(DEV), act)
+    REF.expert_linear(want, x, token_of, w, starts, act)
+    close(out, want, torch.bfloat16, scale=4.0)
+    assert K.tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_gate_and_activation(K, dtype):
     o, wide = rand(13, 70, dtype=dtype, seed=1), rand(13, 200, dtype=dtype, seed=2)

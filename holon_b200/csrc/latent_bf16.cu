@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t lb_pack(float lo, float hi) {
 }
 
 template <int R, int W>
-__global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
+__global__ void __launch_bounds__(W * 32, 1) latent_attention_bf16_kernel(
         bf16* __restrict__ out, float* __restrict__ scratch, const bf16* __restrict__ qa, const bf16* __restrict__ cache,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int row1, int heads,
@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(W * 32) latent_attention_bf16_kernel(
                 float sq[2 * NP][4];
 #pragma unroll
                 for (int i = 0; i < 2 * NP; ++i) { sq[i][0] = sq[i][1] = sq[i][2] = sq[i][3] = 0.f; }
+#pragma unroll 2
                 for (; kk + 32 <= dk; kk += 32) {
                     uint32_t a0[4], a1[4];
                     lb_ldsm4(a0, qs + (size_t)(group * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);

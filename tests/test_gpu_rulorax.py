@@ -414,3 +414,26 @@ def test_greedy_generation_through_the_engine(model, dtype, graphs):
             ids.append(token)
     # bfloat16: rounding may tip a router's close call and with it a token; never more than a few of the sixty
     assert len(off) <= (0 if dtype == "float32" else 4), off
+
+
+def test_generate_on_the_command_line(tmp_path, capsys):
+    """`holon-b200 generate` with the engine's own sizing of the cache (activation peaks measured on the largest step)."""
+    import json
+
+    from holon_b200 import cli
+    folder = make_folder(tmp_path, "a", seed=8)
+    config, weights = plain.read_folder(folder)
+    assert cli.main(["generate", str(folder), "--prompt-ids", "5,17,3,90,12,7", "--prompt-ids", "9 8 7 6", "--max-tokens", "6",
+                     "--dtype", "float32", "--max-model-len", "128", "--max-seqs", "4", "--max-step-tokens", "128", "--ignore-eos",
+                     "--memory-fraction", "0.05"]) == 0
+    captured = capsys.readouterr()
+    assert "holon-b200: memory: weights" in captured.err and "cache pools" in captured.err
+    lines = [json.loads(line) for line in captured.out.splitlines()]
+    assert [o["prompt_ids"] for o in lines] == [[5, 17, 3, 90, 12, 7], [9, 8, 7, 6]]
+    for o in lines:
+        ids = list(o["prompt_ids"])
+        assert len(o["token_ids"]) == 6
+        for token in o["token_ids"]:
+            logits = plain.forward(config, weights, ids)[-1]
+            assert float(logits.max() - logits[token]) <= 1e-3 * float(logits.std()), (len(ids), token)
+            ids.append(token)

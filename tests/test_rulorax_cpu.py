@@ -141,3 +141,37 @@ def test_greedy_generation_through_the_scheduler(model):
             second = float(logits.topk(2).values[1])
             assert token == best or float(logits[best]) - second < 1e-3, (len(ids), token, best)
             ids.append(token)
+
+
+def test_the_command_line_serves_the_design(tmp_path, capsys, monkeypatch):
+    """`random-model` writes a folder with every tensor of the design (hyper-connection coefficients near neutral, in
+    the engine as 32-bit), `models` lists it, and `generate` produces the plain implementation's greedy tokens (on the
+    CPU, with the plain kernel table in the CUDA kernels' place)."""
+    import json
+
+    import holon_b200.engine as engine_module
+    from holon_b200 import cli
+
+    class CpuEngine(engine_module.Engine):
+        def __init__(self, config):
+            config.device, config.state_memory = "cpu", 1 << 22
+            super().__init__(config, kernels=RefKernels())
+    monkeypatch.setattr(engine_module, "Engine", CpuEngine)
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(CONFIGS["a"]))
+    assert cli.main(["random-model", str(config), str(tmp_path / "m"), "--seed", "3"]) == 0
+    folder = capsys.readouterr().out.strip()
+    stored, weights = plain.read_folder(folder)
+    assert set(weights) == {name for name, _ in tensor_table(CONFIGS["a"])}
+    assert float((weights["l0.hc1.mix"] - torch.eye(3, dtype=torch.float64)).abs().max()) < 0.3
+    assert cli.main(["models"]) == 0
+    assert "Rulorax" in capsys.readouterr().out.split()
+    assert cli.main(["generate", folder, "--prompt-ids", "5,17,3,44,9", "--max-tokens", "4", "--dtype", "float32", "--max-model-len",
+                     "64", "--max-seqs", "2", "--max-step-tokens", "32", "--page-size", "8", "--ignore-eos"]) == 0
+    out = json.loads(capsys.readouterr().out.splitlines()[0])
+    ids = [5, 17, 3, 44, 9]
+    for token in out["token_ids"]:
+        logits = plain.forward(stored, weights, ids)[-1]
+        assert token == int(logits.argmax()) or float(logits.max() - logits[token]) < 1e-4
+        ids.append(token)
+    assert len(out["token_ids"]) == 4

@@ -51,6 +51,11 @@ RX_C = {"architecture": "Rulorax", "width": 128, "vocab": 300, "norm": {"eps": 1
 RX_D = {"architecture": "Rulorax", "width": 48, "vocab": 97, "norm": {"eps": 1e-5}, "streams": 5, "layers": [
     _layer(_mixer(2, 48, 16, 16, 64, 5000.0, 3.0), _moe(1, 1, 1.0, 32)),
     _layer(_mixer(2, 48, 16, 16, 64, 5000.0, 3.0), {"kind": "dense", "ff": 64})]}
+# E: a latent of 160 + 16 (two column parts a row group in the tensor-core attention), five heads, two streams.
+RX_E = {"architecture": "Rulorax", "width": 96, "vocab": 263, "norm": {"eps": 1e-5}, "streams": 2, "layers": [
+    _layer(_mixer(5, 24, 16, 40, 160, 20000.0, 2.5), _moe(4, 2, 1.2, 72, shared=40)),
+    _layer(_mixer(5, 24, 16, 40, 160, 20000.0, 2.5, kv_from=0), _moe(4, 2, 1.2, 72, shared=40)),
+    _layer(_mixer(3, 32, 32, 32, 160, 1000.0, 2.5), {"kind": "dense", "ff": 128})]}
 CONFIGS = {"a": RX_A, "b": RX_B, "c": RX_C, "d": RX_D}
 
 

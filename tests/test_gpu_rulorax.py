@@ -15,7 +15,7 @@ from holon_b200.engine.batch import Rows
 from holon_b200.replay import Replayer
 from ref_kernels import RefKernels
 from replay_tools import mixed_trace, portions, run
-from rulorax_tools import CONFIGS, compare, exact_logits, make_folder
+from rulorax_tools import CONFIGS, RX_E, compare, exact_logits, make_folder
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -437,3 +437,19 @@ def test_generate_on_the_command_line(tmp_path, capsys):
             logits = plain.forward(config, weights, ids)[-1]
             assert float(logits.max() - logits[token]) <= 1e-3 * float(logits.std()), (len(ids), token)
             ids.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_then_decoding(tmp_path, dtype):
+    """700 tokens in one step (hundreds of rows an expert: the prompt kernels), cut in two portions at an odd place, and
+    40 tokens one by one over eleven pages (the keys of a one-token row in parts), with a latent wider than 128."""
+    folder = make_folder(tmp_path, "e", seed=4, config=RX_E)
+    ids = random_prompt(RX_E["vocab"], 740, 21)
+    want = {"x": exact_logits(folder, ids), "y": None}
+    want["y"] = want["x"]
+    r = Replayer(str(folder), dtype, max_tokens=1536)
+    steps = [([("x", ids[:700])], [])] + [([("x", [t])], []) for t in ids[700:]]
+    compare(run(r, steps), {"x": want["x"]}, dtype)
+    steps = [([("y", ids[:333])], []), ([("y", ids[333:700]), ("x", ids[700:701])], [])] + [([("y", [t])], []) for t in ids[700:]]
+    got = run(r, steps)
+    compare({k: v for k, v in got.items() if k[0] == "y"}, {"y": want["y"]}, dtype)

@@ -445,8 +445,8 @@ def test_a_long_prompt_then_decoding(tmp_path, dtype):
     40 tokens one by one over eleven pages (the keys of a one-token row in parts), with a latent wider than 128."""
     folder = make_folder(tmp_path, "e", seed=4, config=RX_E)
     ids = random_prompt(RX_E["vocab"], 740, 21)
-    want = {"x": exact_logits(folder, ids), "y": None}
-    want["y"] = want["x"]
+    exact = exact_logits(folder, ids)
+    want = {"x": exact, "y": exact}
     r = Replayer(str(folder), dtype, max_tokens=1536)
     steps = [([("x", ids[:700])], [])] + [([("x", [t])], []) for t in ids[700:]]
     compare(run(r, steps), {"x": want["x"]}, dtype)

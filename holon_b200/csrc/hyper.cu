@@ -14,7 +14,7 @@ struct hc_coef {
 };
 
 template <typename TD, typename TW, int S>
-__global__ void hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const float* __restrict__ src,
+__global__ void __launch_bounds__((S > 0 && S <= 4) ? 1024 : 256) hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const float* __restrict__ src,
                                       const TD* __restrict__ y, const float* __restrict__ mix,
                                       const float* __restrict__ outc, const float* __restrict__ inc,
                                       const TW* __restrict__ weight, float eps, float offset,
@@ -25,14 +25,68 @@ __global__ void hyper_mix_norm_kernel(TD* __restrict__ out, float* xs, const flo
     const int n = S > 0 ? S : streams;
     const int r = blockIdx.x;
     const size_t t = index ? (size_t)index[r] : (size_t)r;
+    const bool fold = y != nullptr, write = index == nullptr && (fold || src != nullptr);
+    float* xr = xs + t * (size_t)n * dim;
+    if constexpr (S > 0 && S <= 4) {
+        if (dim <= (int)blockDim.x * 4) {
+            // A row that the block's threads hold whole (four columns a thread): coefficients straight from global
+            // memory, every load of the row in flight at once, the norm's weight read before the block-wide sum; the
+            // values and their order are those of the general path below.
+            float cm[S * S], co[S], ci[S];
+#pragma unroll
+            for (int i = 0; i < S * S; ++i) cm[i] = mix ? __ldg(mix + i) : 0.f;
+#pragma unroll
+            for (int i = 0; i < S; ++i) { co[i] = outc ? __ldg(outc + i) : 0.f; ci[i] = inc ? __ldg(inc + i) : 1.f; }
+            float old[4][S], yv[4], wv[4], u[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                if (i < dim) {
+#pragma unroll
+                    for (int q = 0; q < S; ++q) old[k][q] = src ? src[t * dim + i] : xr[(size_t)q * dim + i];
+                    yv[k] = fold ? to_f32(y[t * dim + i]) : 0.f;
+                    wv[k] = to_f32(weight[i]) + offset;
+                }
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                u[k] = 0.f;
+                if (i < dim) {
+#pragma unroll
+                    for (int q = 0; q < S; ++q) {
+                        float v;
+                        if (fold) {
+                            v = 0.f;
+#pragma unroll
+                            for (int p = 0; p < S; ++p) v = fmaf(cm[p * S + q], old[k][p], v);
+                            v = fmaf(co[q], yv[k], v);
+                        } else {
+                            v = old[k][q];
+                        }
+                        if (write) xr[(size_t)q * dim + i] = v;
+                        u[k] = fmaf(ci[q], v, u[k]);
+                    }
+                    ss += u[k] * u[k];
+                }
+            }
+            const float rstd = rsqrtf(block_sum(ss, scratch) / (float)dim + eps);
+            TD* o = out + (size_t)r * dim;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                if (i < dim) o[i] = from_f32<TD>(u[k] * rstd * wv[k]);
+            }
+            return;
+        }
+    }
     for (int i = threadIdx.x; i < n * n; i += blockDim.x) c.mix[i] = mix ? mix[i] : 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         c.out[i] = outc ? outc[i] : 0.f;
         c.in[i] = inc ? inc[i] : 1.f;
     }
     __syncthreads();
-    const bool fold = y != nullptr, write = index == nullptr && (fold || src != nullptr);
-    float* xr = xs + t * (size_t)n * dim;
     float ss = 0.f;
     constexpr int NS = S > 0 ? S : HC_MAX_STREAMS;
     constexpr int U = S > 0 && S <= 4 ? 4 : 1;              // columns a thread has in flight at once
@@ -86,7 +140,9 @@ template <typename TD, typename TW>
 static int hyper_launch(void* out, float* xs, const float* src, const void* y, const float* mix, const float* outc,
                         const float* inc, const void* weight, float eps, float offset, const int32_t* index, int rows,
                         int dim, int streams, cudaStream_t s) {
-    const int threads = dim >= 2048 ? 512 : dim >= 512 ? 256 : 128;
+    // up to four streams: four columns a thread hold a whole row of up to 4,096; more streams: the kernel with many registers
+    const int wide = dim > 2048 && rows <= 512 ? 1024 : dim > 1024 ? 512 : dim > 512 ? 256 : 128;   // (many rows: blocks of 512 fill the SMs better)
+    const int threads = streams <= 4 ? wide : (wide < 256 ? wide : 256);
     const size_t smem = (size_t)dim * sizeof(float);
 #define HC_GO(S_) hyper_mix_norm_kernel<TD, TW, S_><<<rows, threads, smem, s>>>((TD*)out, xs, src, (const TD*)y, mix, outc, \
         inc, (const TW*)weight, eps, offset, index, dim, streams)

@@ -45,10 +45,12 @@ def dev(*tensors):
 
 
 # ---------------------------------------------------------------- hyper-connections
-@pytest.mark.parametrize("streams", [1, 2, 3, 4, 7])
+@pytest.mark.parametrize("streams,dim", [(1, 200), (2, 200), (3, 200), (4, 200), (7, 200), (4, 2048), (3, 2560), (2, 5000), (8, 2048), (11, 3000)])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_hyper_mix_norm(K, streams, dtype):
-    t, dim = 6, 200
+def test_hyper_mix_norm(K, streams, dim, dtype):
+    """(Rows of up to 4,096 columns and four streams are held whole by the block's threads; wider rows and more streams
+    take the general path, the latter with fewer threads.)"""
+    t = 6
     xs, src, y = rand(t, streams, dim, seed=1), rand(t, dim, seed=2), rand(t, dim, dtype=dtype, seed=3)
     mix, outc, inc = torch.eye(streams) + rand(streams, streams, seed=4) * 0.3, 1 + rand(streams, seed=5) * 0.3, rand(streams, seed=6)
     w = (1 + rand(dim, seed=7) * 0.1).to(dtype)

@@ -1,0 +1,337 @@
+// Mixers whose memory is a matrix per head instead of a cache of keys: S [key channel, value channel] in 32-bit per
+// request slot and head, updated token by token,
+//     S <- diag(g_t) S                      (g_t: a decay per key channel and token, or one fixed decay per head)
+//     u  = beta_t (v_t - S^T k_t)           (the delta rule; without beta: u = v_t)
+//     S <- S + k_t u^T,      o_t = S^T q_t  (the read-out sees the token's own write)
+// and the kernels around that scan: what turns a layer's first product into q, k, v, decays and gates (a short causal
+// convolution over time with its carried inputs, activations, unit vectors, rotation), and the per-head norm with the
+// output gate behind the scan. Everything that enters the recurrence is 32-bit here, whatever the engine's dtype.
+#include "common.cuh"
+
+// The row b with query_start[b] <= t < query_start[b + 1].
+__device__ __forceinline__ int row_of_token(const int32_t* __restrict__ query_start, int rows, int t) {
+    int lo = 0, hi = rows;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (query_start[mid] <= t) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------- the scan
+// grid (rows, heads, column tiles); a thread owns the key channels d = i * P + p (i < DPT) of one value column, the P
+// threads of a column are neighbouring lanes. Tokens are staged in shared memory SC_TB at a time, so the loop over a
+// stage's tokens has no block-wide barrier: a token costs its multiply-adds and two sums over P lanes.
+#define SC_TB 8
+
+template <int DPT>
+__global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qk, const float* __restrict__ v,
+                                      const float* __restrict__ decay, const float* __restrict__ head_decay,
+                                      const float* __restrict__ beta, float* __restrict__ state,
+                                      const int32_t* __restrict__ query_start, const int32_t* __restrict__ row_slot,
+                                      int heads, int kv_heads, int dim, int vdim, int P, int VT, int tb) {
+    extern __shared__ float sm[];
+    const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * VT;
+    const int hk = h / (heads / kv_heads);
+    const int DP = P * DPT;
+    const int p = threadIdx.x % P, cl = threadIdx.x / P, c = c0 + cl;
+    const bool col = cl < VT && c < vdim;
+    const int t0 = query_start[b], n = query_start[b + 1] - t0;
+    float* S_g = state + ((size_t)row_slot[b] * heads + h) * dim * vdim;
+    float* sq = sm;                          // [tb][DP]
+    float* sk = sq + tb * DP;                // [tb][DP]
+    float* sg = sk + tb * DP;                // [tb][DP]   (per-channel decays only)
+    float* sv = sg + (decay ? tb * DP : 0);  // [tb][VT]
+    float* sb = sv + tb * VT;                // [tb]
+    float S[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = i * P + p;
+        S[i] = col && d < dim ? S_g[(size_t)d * vdim + c] : 0.f;
+    }
+    const float fixed = head_decay ? head_decay[h] : 1.f;
+    for (int j0 = 0; j0 < n; j0 += tb) {
+        const int m = min(tb, n - j0);
+        __syncthreads();                                            // the stage before is read
+        for (int e = threadIdx.x; e < m * DP; e += blockDim.x) {
+            const int j = e / DP, d = e - j * DP;
+            const size_t t = (size_t)(t0 + j0 + j);
+            const bool in = d < dim;
+            sq[e] = in ? qk[((t * 2) * kv_heads + hk) * dim + d] : 0.f;
+            sk[e] = in ? qk[((t * 2 + 1) * kv_heads + hk) * dim + d] : 0.f;
+            if (decay) sg[e] = in ? decay[(t * heads + h) * dim + d] : 1.f;
+        }
+        for (int e = threadIdx.x; e < m * VT; e += blockDim.x) {
+            const int j = e / VT, x = e - j * VT;
+            sv[e] = c0 + x < vdim ? v[((size_t)(t0 + j0 + j) * heads + h) * vdim + c0 + x] : 0.f;
+        }
+        if ((int)threadIdx.x < m) sb[threadIdx.x] = beta ? beta[(size_t)(t0 + j0 + threadIdx.x) * heads + h] : 1.f;
+        __syncthreads();
+        for (int j = 0; j < m; ++j) {
+            const float* kj = sk + j * DP + p;
+            const float* qj = sq + j * DP + p;
+            float u = cl < VT ? sv[j * VT + cl] : 0.f;               // (threads past the tile carry zeros: the sums below are warp-wide)
+            if (decay) {
+                const float* gj = sg + j * DP + p;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) S[i] *= gj[i * P];
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) S[i] *= fixed;
+            }
+            if (beta) {
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT; i += 2) { a0 = fmaf(S[i], kj[i * P], a0); a1 = fmaf(S[i + 1], kj[(i + 1) * P], a1); }
+                float a = a0 + a1;
+                for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                u = sb[j] * (u - a);
+            }
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT; i += 2) {
+                S[i] = fmaf(kj[i * P], u, S[i]);
+                S[i + 1] = fmaf(kj[(i + 1) * P], u, S[i + 1]);
+                o0 = fmaf(S[i], qj[i * P], o0);
+                o1 = fmaf(S[i + 1], qj[(i + 1) * P], o1);
+            }
+            float o = o0 + o1;
+            for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (p == 0 && col) out[((size_t)(t0 + j0 + j) * heads + h) * vdim + c] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = i * P + p;
+        if (col && d < dim) S_g[(size_t)d * vdim + c] = S[i];
+    }
+}
+
+extern "C" int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
+                                 const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
+                                 int rows, int heads, int kv_heads, int dim, int vdim, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("recurrent_scan: %d heads are no multiple of %d key heads", heads, kv_heads);
+    if (dim < 1 || dim > 1024 || vdim < 1) HB_REFUSE("recurrent_scan: key size %d (1 to 1024), value size %d", dim, vdim);
+    if ((decay != nullptr) == (head_decay != nullptr)) HB_REFUSE("recurrent_scan: give decays per channel and token, or one per head");
+    if (rows > 65535 * 32 || heads > 65535) HB_REFUSE("recurrent_scan: %d rows, %d heads", rows, heads);
+    const int dpt = dim <= 64 ? 8 : dim <= 128 ? 16 : 32;
+    int P = 1;
+    while (P * dpt < dim) P <<= 1;
+    const int unit = 32 / P > 1 ? 32 / P : 1;                         // columns a warp holds
+    int VT = vdim < 256 / P ? vdim : 256 / P;
+    if (VT < 1) VT = 1;
+    const int threads = ((VT + unit - 1) / unit) * unit * P;
+    const int tiles = (vdim + VT - 1) / VT;
+    const int DP = P * dpt;
+    const int per_token = (decay ? 3 : 2) * DP + VT + 1;
+    int tb = 48 * 1024 / 4 / per_token;
+    if (tb > SC_TB) tb = SC_TB;
+    if (tb < 1) HB_REFUSE("recurrent_scan: key size %d needs more shared memory than a block has", dim);
+    if (tb > threads) tb = threads;
+    const size_t smem = (size_t)tb * per_token * sizeof(float);
+    dim3 grid(rows, heads, tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_SCAN(D) recurrent_scan_kernel<D><<<grid, threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, \
+    query_start, row_slot, heads, kv_heads, dim, vdim, P, VT, tb)
+    if (dpt == 8) HB_SCAN(8); else if (dpt == 16) HB_SCAN(16); else HB_SCAN(32);
+#undef HB_SCAN
+    HB_LAUNCH_CHECK("recurrent_scan");
+    return 0;
+}
+
+// ---------------------------------------------------------------- what the delta-rule mixer's first product becomes
+// A token's row of `first` holds [q (kv_heads dim) | k (kv_heads dim) | v (heads vdim) | b (heads) | a1 (ra) | g1 (rg)].
+// q, k, v pass a causal convolution over time (weights conv [channels, taps], the last tap the token's own; inputs
+// before the step's first token of the row come from conv_state [slots, taps - 1, channels], oldest first) and silu;
+// q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale. beta = sigmoid(b).
+// decay[h, d] = exp(-exp(rate_log[h]) softplus(a2[h dim + d] . a1 + dt_bias[h dim + d])), gate = sigmoid(g2 . g1).
+// One block per token.
+template <typename T>
+__global__ void delta_prepare_kernel(float* __restrict__ qk, float* __restrict__ v, float* __restrict__ beta,
+                                     float* __restrict__ decay, float* __restrict__ gate, const T* __restrict__ first,
+                                     int ld, const T* __restrict__ conv, int taps, const T* __restrict__ conv_state,
+                                     const T* __restrict__ a2, const float* __restrict__ dt_bias, const float* __restrict__ rate_log,
+                                     const T* __restrict__ g2, const int32_t* __restrict__ query_start,
+                                     const int32_t* __restrict__ row_slot, int rows, int heads, int kv_heads, int dim,
+                                     int vdim, int ra, int rg, float q_scale, float unit_eps) {
+    extern __shared__ float sm[];
+    const int t = blockIdx.x;
+    const int b = row_of_token(query_start, rows, t);
+    const int t0 = query_start[b];
+    const int nq = kv_heads * dim, nv = heads * vdim, C = 2 * nq + nv;
+    float* y = sm;                 // [C] after convolution and silu
+    float* low = y + C;            // [ra + rg] the low-rank inputs
+    const T* st = conv_state ? conv_state + (size_t)row_slot[b] * (taps - 1) * C : nullptr;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;                           // how many tokens before t
+            float x;
+            if (t - back >= t0) x = to_f32(first[(size_t)(t - back) * ld + c]);
+            else x = to_f32(st[(size_t)(taps - 1 + (t - back - t0)) * C + c]);
+            acc = fmaf(to_f32(conv[(size_t)c * taps + j]), x, acc);
+        }
+        y[c] = silu_f(acc);
+    }
+    const T* row = first + (size_t)t * ld;
+    for (int i = threadIdx.x; i < ra + rg; i += blockDim.x) low[i] = to_f32(row[C + heads + i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int g = warp; g < 2 * kv_heads; g += warps) {               // unit vectors: q heads, then k heads
+        const float* x = y + (size_t)g * dim;
+        float ss = 0.f;
+        for (int d = lane; d < dim; d += 32) ss += x[d] * x[d];
+        ss = warp_sum(ss);
+        const float f = rsqrtf(ss + unit_eps) * (g < kv_heads ? q_scale : 1.f);
+        for (int d = lane; d < dim; d += 32) qk[((size_t)t * 2 * kv_heads + g) * dim + d] = x[d] * f;
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) v[(size_t)t * nv + i] = y[2 * nq + i];
+    for (int i = threadIdx.x; i < heads; i += blockDim.x) beta[(size_t)t * heads + i] = sigmoid_f(to_f32(row[C + i]));
+    for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+        float a = dt_bias[i];
+        const T* w = a2 + (size_t)i * ra;
+        for (int r = 0; r < ra; ++r) a = fmaf(to_f32(w[r]), low[r], a);
+        decay[(size_t)t * heads * dim + i] = expf(-expf(rate_log[i / dim]) * softplus_f(a));
+    }
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        float a = 0.f;
+        const T* w = g2 + (size_t)i * rg;
+        for (int r = 0; r < rg; ++r) a = fmaf(to_f32(w[r]), low[ra + r], a);
+        gate[(size_t)t * nv + i] = sigmoid_f(a);
+    }
+}
+
+extern "C" int hb_delta_prepare(float* qk, float* v, float* beta, float* decay, float* gate, const void* first, int dtype,
+                                int ld, const void* conv, int taps, const void* conv_state, const void* a2,
+                                const float* dt_bias, const float* rate_log, const void* g2, const int32_t* query_start,
+                                const int32_t* row_slot, int rows, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                int ra, int rg, float q_scale, float unit_eps, hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (taps < 1 || (taps > 1 && !conv_state)) HB_REFUSE("delta_prepare: %d taps need the carried inputs", taps);
+    const int C = 2 * kv_heads * dim + heads * vdim;
+    const size_t smem = (size_t)(C + ra + rg) * sizeof(float);
+    if (smem > 200 * 1024) HB_REFUSE("delta_prepare: %d channels are more than a block's shared memory holds", C);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS(T) (const T*)first, ld, (const T*)conv, taps, (const T*)conv_state, (const T*)a2, dt_bias, \
+    rate_log, (const T*)g2, query_start, row_slot, rows, heads, kv_heads, dim, vdim, ra, rg, q_scale, unit_eps
+    if (dtype == HB_F32) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        delta_prepare_kernel<float><<<tokens, 256, smem, s>>>(qk, v, beta, decay, gate, HB_ARGS(float));
+    } else if (dtype == HB_BF16) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        delta_prepare_kernel<bf16><<<tokens, 256, smem, s>>>(qk, v, beta, decay, gate, HB_ARGS(bf16));
+    } else HB_REFUSE("delta_prepare: dtype %d", dtype);
+#undef HB_ARGS
+    HB_LAUNCH_CHECK("delta_prepare");
+    return 0;
+}
+
+// The carried inputs of the convolution after a step: the last taps - 1 inputs of (what was carried, the row's tokens).
+// A thread per (row, channel); entry i takes what lies n places further on, so ascending i reads nothing written.
+template <typename T>
+__global__ void conv_carry_kernel(T* __restrict__ conv_state, const T* __restrict__ first, int ld, int C, int keep,
+                                  const int32_t* __restrict__ query_start, const int32_t* __restrict__ row_slot) {
+    const int b = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int t0 = query_start[b], n = query_start[b + 1] - t0;
+    T* st = conv_state + (size_t)row_slot[b] * keep * C;
+    for (int i = 0; i < keep; ++i) {
+        const int src = n - keep + i;                                // among the row's tokens; negative: carried before
+        st[(size_t)i * C + c] = src >= 0 ? first[(size_t)(t0 + src) * ld + c] : st[(size_t)(keep + src) * C + c];
+    }
+}
+
+extern "C" int hb_conv_carry(void* conv_state, const void* first, int dtype, int ld, int channels, int taps,
+                             const int32_t* query_start, const int32_t* row_slot, int rows, hb_stream stream) {
+    if (rows == 0 || taps <= 1) return 0;
+    if (rows > 65535) HB_REFUSE("conv_carry: %d rows are above 65535", rows);
+    dim3 grid((channels + 127) / 128, rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) conv_carry_kernel<float><<<grid, 128, 0, s>>>((float*)conv_state, (const float*)first, ld, channels, taps - 1, query_start, row_slot);
+    else if (dtype == HB_BF16) conv_carry_kernel<bf16><<<grid, 128, 0, s>>>((bf16*)conv_state, (const bf16*)first, ld, channels, taps - 1, query_start, row_slot);
+    else HB_REFUSE("conv_carry: dtype %d", dtype);
+    HB_LAUNCH_CHECK("conv_carry");
+    return 0;
+}
+
+// ---------------------------------------------------------------- what the retention mixer's first product becomes
+// A token's row of `first` holds [q (heads dim) | k (heads dim) | v (heads vdim) | ...]. q and k turn by the token's
+// position (the first rot_dims channels of a head, half-split pairs, table [positions, rot_dims]: cosines then sines),
+// k is then scaled. One block per token.
+template <typename T>
+__global__ void retention_prepare_kernel(float* __restrict__ qk, float* __restrict__ v, const T* __restrict__ first, int ld,
+                                         const int32_t* __restrict__ positions, const float* __restrict__ table,
+                                         int rot_dims, int max_positions, int heads, int dim, int vdim, float k_scale) {
+    const size_t t = blockIdx.x;
+    const T* row = first + t * ld;
+    const int pos = min(max(positions[t], 0), max_positions > 0 ? max_positions - 1 : 0);
+    const float* cs = table ? table + (size_t)pos * rot_dims : nullptr;
+    const int half = rot_dims >> 1, nq = heads * dim;
+    for (int e = threadIdx.x; e < 2 * nq; e += blockDim.x) {
+        const int d = e % dim;
+        float x = to_f32(row[e]);
+        if (d < half) x = x * cs[d] - to_f32(row[e + half]) * cs[half + d];
+        else if (d < rot_dims) x = x * cs[d - half] + to_f32(row[e - half]) * cs[d];
+        qk[t * 2 * nq + e] = e >= nq ? x * k_scale : x;
+    }
+    for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) v[t * heads * vdim + e] = to_f32(row[2 * nq + e]);
+}
+
+extern "C" int hb_retention_prepare(float* qk, float* v, const void* first, int dtype, int ld, const int32_t* positions,
+                                    const float* table, int rot_dims, int max_positions, int tokens, int heads, int dim,
+                                    int vdim, float k_scale, hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (rot_dims % 2 || rot_dims < 0 || rot_dims > dim) HB_REFUSE("retention_prepare: %d rotated channels of %d", rot_dims, dim);
+    if (rot_dims && !table) HB_REFUSE("retention_prepare: a rotation needs its table");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) retention_prepare_kernel<float><<<tokens, 256, 0, s>>>(qk, v, (const float*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
+    else if (dtype == HB_BF16) retention_prepare_kernel<bf16><<<tokens, 256, 0, s>>>(qk, v, (const bf16*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
+    else HB_REFUSE("retention_prepare: dtype %d", dtype);
+    HB_LAUNCH_CHECK("retention_prepare");
+    return 0;
+}
+
+// ---------------------------------------------------------------- per-head norm and output gate behind the scan
+// out[t, h, :] = o / sqrt(mean(o^2) + eps) * weight * gate. `weight` [vdim] or null; the gate is either a ready
+// multiplier in 32-bit (gate_mul [tokens, heads vdim]) or silu of a pre-activation in the engine's dtype (gate_pre, rows
+// `ld` apart). One warp per (token, head).
+template <typename T>
+__global__ void head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const float* __restrict__ weight,
+                                      const float* __restrict__ gate_mul, const T* __restrict__ gate_pre, long ld,
+                                      float eps, long items, int heads, int vdim) {
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int lane = threadIdx.x & 31;
+    const long t = item / heads;
+    const int h = (int)(item - t * heads);
+    const float* x = o + item * vdim;
+    float ss = 0.f;
+    for (int d = lane; d < vdim; d += 32) ss += x[d] * x[d];
+    const float f = rsqrtf(warp_sum(ss) / vdim + eps);
+    for (int d = lane; d < vdim; d += 32) {
+        float y = x[d] * f;
+        if (weight) y *= weight[d];
+        if (gate_mul) y *= gate_mul[item * vdim + d];
+        else if (gate_pre) y *= silu_f(to_f32(gate_pre[t * ld + (long)h * vdim + d]));
+        out[item * vdim + d] = from_f32<T>(y);
+    }
+}
+
+extern "C" int hb_head_norm_gate(void* out, const float* o, int dtype, const float* weight, const float* gate_mul,
+                                 const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim,
+                                 hb_stream stream) {
+    const long items = (long)tokens * heads;
+    if (items == 0) return 0;
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, s>>>((float*)out, o, weight, gate_mul, (const float*)gate_pre, ld, eps, items, heads, vdim);
+    else if (dtype == HB_BF16) head_norm_gate_kernel<bf16><<<blocks, 128, 0, s>>>((bf16*)out, o, weight, gate_mul, (const bf16*)gate_pre, ld, eps, items, heads, vdim);
+    else HB_REFUSE("head_norm_gate: dtype %d", dtype);
+    HB_LAUNCH_CHECK("head_norm_gate");
+    return 0;
+}

@@ -1,0 +1,132 @@
+"""Mixers whose memory is a matrix per head and request instead of a cache of keys.
+
+Both keep S [key channel, value channel] in 32-bit per request slot and head (`SlotState`), zero at admission, and
+update it token by token with the kernel table's `recurrent_scan`:
+
+    S ← diag(g_t) S;   u = β_t (v_t − Sᵀ k_t)  (or u = v_t);   S ← S + k_t uᵀ;   o_t = Sᵀ q_t.
+
+`Retention`: one fixed decay per head, no β (linear attention without softmax or denominator); q and k turned by the
+position, k scaled by dim^(−1/2); each head's o divided by its root mean square, times silu(W_g x), then W_o.
+
+`GatedDelta`: the delta rule with a decay per key channel and token. q, k, v pass a short causal convolution over time
+(its last taps − 1 inputs are carried per request, a second `SlotState`) and silu; q and k become unit vectors per head,
+q times dim^(−1/2); β = sigmoid(W_b x); g = exp(−exp(A_log) · softplus(W_a2 W_a1 x + dt_bias)); each head's o under an
+RMS norm with one weight shared by the heads, times sigmoid(W_g2 W_g1 x), then W_o. Query/key heads may be fewer than
+value heads (head h reads key head h // (heads / kv_heads)).
+
+Everything that enters the recurrence is 32-bit (the scan's inputs are made in 32-bit from the first product's rows);
+the products themselves are the engine's. All first projections of a mixer are one merged product.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import PartRef
+from .base import BuildContext, Part, SlotState
+from .linear import Linear
+
+
+class _MatrixState(Part):
+    """What both mixers share: no paged cache, one state matrix per head, loadable names without the children's."""
+
+    def cache(self):
+        return None
+
+    def _strip(self, prefix: str, name: str) -> str:
+        for child in ("first.", "out."):
+            if name.startswith(prefix + child):
+                return prefix + name[len(prefix + child):]
+        return name
+
+    def loadables(self, prefix: str = ""):
+        for name, p, rows in super().loadables(prefix):
+            yield self._strip(prefix, name), p, rows
+
+
+class Retention(_MatrixState):
+    def __init__(self, ctx: BuildContext, *, heads: int, dim: int, vdim: int, decay: tuple[float, ...], eps: float,
+                 hidden: int, position: PartRef | None, layer: int = 0) -> None:
+        super().__init__()
+        if len(decay) != heads:
+            raise ValueError(f"retention: {len(decay)} decays for {heads} heads")
+        self.ctx, self.heads, self.dim, self.vdim, self.eps = ctx, heads, dim, vdim, float(eps)
+        self.decay = tuple(float(d) for d in decay)
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {
+            "q": heads * dim, "k": heads * dim, "v": heads * vdim, "g": heads * vdim}))
+        self.out = self.add_child("out", Linear(ctx, "weight", heads * vdim, {"o": hidden}))
+        self.position = self.add_child("position", ctx.part(position, head_dim=dim)) if position else None
+        self._decay = None
+
+    def finalize(self) -> None:
+        super().finalize()
+        if self.first.weight.tensor is not None:
+            self._decay = torch.tensor(self.decay, dtype=torch.float32, device=self.first.weight.tensor.device)
+
+    def slot_states(self):
+        return (SlotState("state", (self.heads, self.dim, self.vdim)),)
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        t, k, ctx, heads, dim, vdim = x.shape[0], self.ctx.kernels, self.ctx, self.heads, self.dim, self.vdim
+        first = self.first.forward(x)                                    # [t, q | k | v | g]
+        qk = ctx.empty(t, 2, heads, dim, dtype=torch.float32)
+        v = ctx.empty(t, heads, vdim, dtype=torch.float32)
+        pos = self.position
+        k.retention_prepare(qk, v, first, step.positions, pos.table if pos else None, pos.rotary_dim if pos else 0,
+                            dim ** -0.5)
+        o = ctx.empty(t, heads, vdim, dtype=torch.float32)
+        k.recurrent_scan(o, qk, v, None, self._decay, None, cache.slots["state"], step.rows)
+        y = ctx.empty(t, heads, vdim)
+        at = 2 * heads * dim + heads * vdim
+        k.head_norm_gate(y, o, None, None, first[:, at:at + heads * vdim], self.eps)
+        return self.out.forward(y.view(t, heads * vdim))
+
+
+class GatedDelta(_MatrixState):
+    UNIT_EPS = 1e-6                       # inside the root of the unit vectors
+
+    def __init__(self, ctx: BuildContext, *, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, decay_rank: int,
+                 gate_rank: int, eps: float, hidden: int, layer: int = 0) -> None:
+        super().__init__()
+        if heads % kv_heads:
+            raise ValueError(f"gated delta: {heads} heads are no multiple of {kv_heads} key heads")
+        if taps < 1:
+            raise ValueError("gated delta: the convolution has at least one tap")
+        self.ctx, self.heads, self.kv_heads, self.dim, self.vdim = ctx, heads, kv_heads, dim, vdim
+        self.taps, self.eps = int(taps), float(eps)
+        nq, nv = kv_heads * dim, heads * vdim
+        self.channels = 2 * nq + nv
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {
+            "q": nq, "k": nq, "v": nv, "b": heads, "a1": decay_rank, "g1": gate_rank}))
+        self.conv = self.add_param("conv", (self.channels, taps), "matrix",
+                                   {"q.conv": (0, nq), "k.conv": (nq, 2 * nq), "v.conv": (2 * nq, self.channels)})
+        self.a2 = self.add_param("a2", (heads * dim, decay_rank), "matrix")
+        self.g2 = self.add_param("g2", (nv, gate_rank), "matrix")
+        self.dt_bias = self.add_param("dt_bias", (heads * dim,), "coef")
+        self.rate_log = self.add_param("A_log", (heads,), "coef")
+        self.gain = self.add_param("norm", (vdim,), "coef")
+        self.out = self.add_child("out", Linear(ctx, "weight", nv, {"o": hidden}))
+
+    def slot_states(self):
+        states = [SlotState("state", (self.heads, self.dim, self.vdim))]
+        if self.taps > 1:
+            dtype = str(self.ctx.dtype).replace("torch.", "")
+            states.append(SlotState("conv", (self.taps - 1, self.channels), dtype))
+        return tuple(states)
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        t, k, ctx = x.shape[0], self.ctx.kernels, self.ctx
+        heads, kvh, dim, vdim = self.heads, self.kv_heads, self.dim, self.vdim
+        f32 = torch.float32
+        first = self.first.forward(x)                                    # [t, q | k | v | b | a1 | g1]
+        qk, v = ctx.empty(t, 2, kvh, dim, dtype=f32), ctx.empty(t, heads, vdim, dtype=f32)
+        beta, decay = ctx.empty(t, heads, dtype=f32), ctx.empty(t, heads, dim, dtype=f32)
+        gate = ctx.empty(t, heads * vdim, dtype=f32)
+        carried = cache.slots.get("conv")
+        k.delta_prepare(qk, v, beta, decay, gate, first, self.conv.tensor, carried, self.a2.tensor, self.dt_bias.tensor,
+                        self.rate_log.tensor, self.g2.tensor, step.rows, dim ** -0.5, self.UNIT_EPS)
+        k.conv_carry(carried, first, self.channels, self.taps, step.rows)
+        o = ctx.empty(t, heads, vdim, dtype=f32)
+        k.recurrent_scan(o, qk, v, decay, None, beta, cache.slots["state"], step.rows)
+        y = ctx.empty(t, heads, vdim)
+        k.head_norm_gate(y, o, self.gain.tensor, gate, None, self.eps)
+        return self.out.forward(y.view(t, heads * vdim))

@@ -22,15 +22,19 @@ class Architecture:
     name: str
     parse: Callable[[Mapping[str, Any]], Any]            # config.json dict -> typed configuration
     recipe: Callable[[Any], ModelSpec]                    # typed configuration -> ModelSpec
+    complete: Callable[[Mapping[str, Any], Mapping[str, tuple]], Mapping[str, Any]] | None = None
+    # (config.json dict, stored tensor name -> shape) -> the dict with the sizes that only a tensor's shape gives
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse, recipe, replace: bool = False) -> Architecture:
+def register_architecture(name: str, parse, recipe, replace: bool = False, complete=None) -> Architecture:
+    """`complete(config, shapes)`: for a design whose config.json leaves some sizes to the stored tensors' shapes; a
+    source that knows its tensors' shapes (a model folder) has them entered before `parse` sees the dict."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is registered already")
-    _ARCHITECTURES[name] = arch = Architecture(name, parse, recipe)
+    _ARCHITECTURES[name] = arch = Architecture(name, parse, recipe, complete)
     return arch
 
 

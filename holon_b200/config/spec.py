@@ -60,9 +60,12 @@ class WeightRule:
 
 @dataclasses.dataclass(frozen=True)
 class ModelSpec:
+    """`layers[i]` None: layer i has no parts of its own (its runs are listed under the layer whose parts it uses, each
+    with a cache entry of its own), so that layer numbers stay the stored tensors' numbers."""
+
     hidden: int
     vocab: int
-    layers: tuple[LayerSpec, ...]
+    layers: tuple[LayerSpec | None, ...]
     order: tuple[Run, ...]
     embed: PartRef
     norm: PartRef
@@ -75,6 +78,8 @@ class ModelSpec:
         for run in self.order:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run order names layer {run.layer}, the model has {len(self.layers)}")
+            if self.layers[run.layer] is None:
+                raise ValueError(f"run order names layer {run.layer}, which has no parts of its own")
             if run.fills:
                 if run.cache in filled:
                     raise ValueError(f"cache entry {run.cache} is filled by two runs")

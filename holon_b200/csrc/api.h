@@ -46,11 +46,13 @@ int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype, const int3
 
 // Attention of the step's new rows over the paged cache, any sizes, on CUDA cores with 32-bit arithmetic.
 // Row b owns query rows query_start[b] .. query_start[b+1], the last ones of its kv_len[b] tokens; a query at position
-// p sees keys j <= p, with window > 0 only p - j < window.
+// p sees keys j <= p, with window > 0 only p - j < window. `sinks` (float [heads], or null): each head's softmax
+// denominator also holds exp(sinks[h]), a weight without key or value that is not scaled; the bfloat16 kernels below that
+// take `sinks` mean the same.
 int hb_attention_generic(void* out, const void* q, const void* kv, int dtype, const int32_t* block_table,
                          int table_stride, const int32_t* row_slot, const int32_t* query_start,
                          const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads, int head_dim,
-                         int pages, int page_size, float scale, int window, hb_stream stream);
+                         int pages, int page_size, float scale, int window, const float* sinks, hb_stream stream);
 
 // bfloat16 attention on tensor cores for rows that bring one token each (rows 0 .. rows - 1 of the batch). The keys of
 // a row are cut into `splits` parts that run side by side; with more than one split, `scratch` must hold
@@ -60,7 +62,7 @@ size_t hb_attention_decode_scratch_floats(int rows, int heads, int head_dim, int
 int hb_attention_decode_bf16(void* out, float* scratch, const void* q, const void* kv, const int32_t* block_table,
                              int table_stride, const int32_t* row_slot, const int32_t* query_start,
                              const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
-                             int page_size, float scale, int window, int splits, hb_stream stream);
+                             int page_size, float scale, int window, int splits, const float* sinks, hb_stream stream);
 
 // The same rows with 2 to 16 splits whose CTAs form a thread-block cluster and merge through distributed shared memory
 // inside the kernel: no scratch, no second kernel. hb_attention_decode_cluster_capacity: clusters of that many CTAs
@@ -86,7 +88,7 @@ int hb_attention_decode_bf16_balanced(void* out, float* scratch, const void* q, 
 int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                               const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
                               int rows, int q_tiles, int heads, int kv_heads, int head_dim, int pages, int page_size,
-                              float scale, int window, hb_stream stream);
+                              float scale, int window, const float* sinks, hb_stream stream);
 
 // The same rows on tcgen05 tensor cores (scores and output in tensor memory, operands by TMA): head_dim 128, page
 // sizes that are multiples of 64. q_tiles: the sum over the rows of ceil(tokens / tile_q); tokens: all tokens of the
@@ -298,6 +300,51 @@ int hb_sample(int32_t* tokens, const float* logits, const float* temperature, co
 // logits by ascending id) as top_ids / top [rows, k]; places beyond the row's finite entries hold id -1 and -inf.
 int hb_logprobs(float* chosen, int32_t* top_ids, float* top, const float* logits, const int32_t* tokens, int rows,
                 int vocab, int k, hb_stream stream);
+
+// Embedding rows times `scale`, plus a row of `pair` [buckets + 1, hidden] chosen by (previous id, id): row
+// (previous * mul_prev + id * mul_cur) mod buckets, or row `buckets` at position 0. `prev` [slots] carries each slot's
+// last id from step to step (read for a row's first token, then set to the row's last id). pair null: none is added.
+int hb_embed_pair(float* out, const void* table, int table_dtype, float scale, const void* pair, const int32_t* ids,
+                  const int32_t* positions, const int32_t* query_start, const int32_t* row_slot, int32_t* prev, int rows,
+                  int tokens, int hidden, int vocab, long mul_prev, long mul_cur, int buckets, hb_stream stream);
+// h [tokens, hidden] (32-bit) += s0 x0 + s1 x1 + s2 x2 + s3 x3 + bias; terms of `dtype`, any of them null.
+int hb_sum_into(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1, float s2,
+                float s3, const void* bias, int dtype, int tokens, int hidden, hb_stream stream);
+// out [tokens, inter] = g sigmoid(alpha g) (u + 1), g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
+// gate_up [tokens, 2 inter] (gate first) and bias [2 inter] (or null).
+int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, float limit, float alpha, int tokens,
+                   int inter, hb_stream stream);
+
+// ---- mixers with a matrix state per head (csrc/recurrent.cu). Rows as for attention: row b brings tokens
+// query_start[b] .. query_start[b + 1] and lives in slot row_slot[b].
+// The scan. qk [tokens, 2, kv_heads, dim] (queries, then keys), v [tokens, heads, vdim], state [slots, heads, dim, vdim],
+// all 32-bit; head h reads key head h / (heads / kv_heads). Per token: S <- g S with g = decay[t, h, :] (per key channel)
+// or head_decay[h] (give exactly one of the two); u = beta[t, h] (v - S^T k) (beta null: u = v); S <- S + k u^T;
+// out[t, h, :] = S^T q. The state is read at the start of a row and written back at its end.
+int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
+                      const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
+                      int heads, int kv_heads, int dim, int vdim, hb_stream stream);
+// A delta-rule mixer's first product, rows [q | k | v | b | a1 | g1] of `dtype`, `ld` apart, becomes the scan's inputs:
+// q, k, v through a causal convolution over time (conv [channels, taps], carried inputs conv_state [slots, taps - 1,
+// channels]) and silu; q, k unit vectors per head (eps unit_eps), q times q_scale; beta = sigmoid(b);
+// decay = exp(-exp(rate_log[h]) softplus(a2 a1 + dt_bias)) [tokens, heads, dim]; gate = sigmoid(g2 g1) [tokens, heads vdim].
+int hb_delta_prepare(float* qk, float* v, float* beta, float* decay, float* gate, const void* first, int dtype, int ld,
+                     const void* conv, int taps, const void* conv_state, const void* a2, const float* dt_bias,
+                     const float* rate_log, const void* g2, const int32_t* query_start, const int32_t* row_slot, int rows,
+                     int tokens, int heads, int kv_heads, int dim, int vdim, int ra, int rg, float q_scale,
+                     float unit_eps, hb_stream stream);
+// conv_state <- the last taps - 1 inputs of each row (what was carried, then the step's tokens). After hb_delta_prepare.
+int hb_conv_carry(void* conv_state, const void* first, int dtype, int ld, int channels, int taps,
+                  const int32_t* query_start, const int32_t* row_slot, int rows, hb_stream stream);
+// A retention mixer's first product, rows [q (heads dim) | k (heads dim) | v (heads vdim) | ...]: q and k turned by the
+// position (as hb_qk_norm_rope_kv_write turns them), k times k_scale, all to 32-bit.
+int hb_retention_prepare(float* qk, float* v, const void* first, int dtype, int ld, const int32_t* positions,
+                         const float* table, int rot_dims, int max_positions, int tokens, int heads, int dim, int vdim,
+                         float k_scale, hb_stream stream);
+// out [tokens, heads, vdim] (`dtype`) = o / sqrt(mean(o^2) + eps) * weight (float [vdim] or null) * gate, the gate a
+// 32-bit multiplier gate_mul [tokens, heads vdim], or silu of gate_pre (rows `ld` apart, `dtype`), or none.
+int hb_head_norm_gate(void* out, const float* o, int dtype, const float* weight, const float* gate_mul,
+                      const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim, hb_stream stream);
 
 #ifdef __cplusplus
 }

@@ -186,7 +186,8 @@ __device__ __forceinline__ void decode_walk(
         unsigned char* smem_raw, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
         size_t part_base, int part_stride, const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const int32_t* __restrict__ table, int t, int heads, int kv_heads, int head_dim, int pages, int page_size,
-        int page_shift, float scale_log2, int hk, int group, int g0, int g, int first, int last, int lo, int n) {
+        int page_shift, float scale_log2, int hk, int group, int g0, int g, int first, int last, int lo, int n,
+        const float* __restrict__ sinks = nullptr) {
     constexpr uint32_t TILE_BYTES = TILE_N * D_PAD * 2;
     const uint32_t q_s = smem_u32(smem_raw);                       // [16][D_PAD]
     const uint32_t k_s = q_s + 16 * D_PAD * 2;                     // [STAGES][64][D_PAD]
@@ -313,6 +314,7 @@ __device__ __forceinline__ void decode_walk(
         }
         const int h = hk * group + g0 + r;
         if (part_stride == 0) {
+            if (sinks && l > 0.f) l += ex2(fmaf(sinks[h], 1.4426950408889634f, -mm * scale_log2));   // the sink: a weight without a value
             out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else if (part_stride < 0) {                               // left in shared memory for the CTA's cluster
             float* stage = wml + 4 * 16 * 2;                        // [16][D_PAD] sums, then [16][2] (max in log2 units, sum)
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(128) decode_kernel(
         const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
         const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
         const int32_t* __restrict__ kv_len, int heads, int kv_heads, int head_dim, int pages, int page_size,
-        int page_shift, float scale_log2, int window, int splits) {
+        int page_shift, float scale_log2, int window, int splits, const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int b = blockIdx.x, split = blockIdx.z;
     const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
@@ -348,7 +350,7 @@ __global__ void __launch_bounds__(128) decode_kernel(
     decode_walk<D_PAD, STAGES>(smem_raw, out, part_o, part_ml, ((size_t)b * heads + (size_t)hk * group + g0) * splits + split,
                                splits > 1 ? splits : 0, q, kv, block_table + (size_t)row_slot[b] * table_stride,
                                query_start[b], heads, kv_heads, head_dim, pages, page_size, page_shift, scale_log2, hk,
-                               group, g0, g, first, last, lo, n);
+                               group, g0, g, first, last, lo, n, sinks);
 }
 
 // The same rows with the splits of a (row, kv head) as one thread-block cluster: each CTA leaves its partial result in
@@ -464,7 +466,7 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
 // order of the sums depends on `count` alone, so equal inputs give equal outputs.
 __device__ __forceinline__ void merge_partials(bf16* __restrict__ out, const float* __restrict__ part_o,
                                                const float* __restrict__ part_ml, size_t base, size_t stride, int count,
-                                               int head_dim) {
+                                               int head_dim, const float* __restrict__ sink = nullptr) {
     __shared__ float red[4];
     __shared__ float sums[4][257];                                   // per warp: up to 256 values and the sum of weights
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -494,7 +496,8 @@ __device__ __forceinline__ void merge_partials(bf16* __restrict__ out, const flo
         __syncthreads();
         const int dd = d0 + (int)threadIdx.x;
         if (dd < head_dim) {
-            const float total = ((sums[0][256] + sums[1][256]) + sums[2][256]) + sums[3][256];
+            float total = ((sums[0][256] + sums[1][256]) + sums[2][256]) + sums[3][256];
+            if (sink && total > 0.f) total += ex2(fmaf(*sink, 1.4426950408889634f, -mm));   // (maxima are kept in log2 units)
             const float v = ((sums[0][threadIdx.x] + sums[1][threadIdx.x]) + sums[2][threadIdx.x]) + sums[3][threadIdx.x];
             out[dd] = __float2bfloat16_rn(total > 0.f ? v / total : 0.f);
         }
@@ -505,10 +508,10 @@ __device__ __forceinline__ void merge_partials(bf16* __restrict__ out, const flo
 // out[t, h, :] from the partial results of (row, head)'s splits, in ascending order.
 __global__ void decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, const int32_t* __restrict__ query_start,
-                                    int heads, int head_dim, int splits) {
+                                    int heads, int head_dim, int splits, const float* __restrict__ sinks) {
     const int b = blockIdx.x, h = blockIdx.y;
     merge_partials(out + ((size_t)query_start[b] * heads + h) * head_dim, part_o, part_ml,
-                   ((size_t)b * heads + h) * splits, 1, splits, head_dim);
+                   ((size_t)b * heads + h) * splits, 1, splits, head_dim, sinks ? sinks + h : nullptr);
 }
 
 template <int D_PAD> static size_t decode_smem(int stages) {
@@ -523,7 +526,8 @@ template <int D_PAD, int STAGES>
 static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* kv,
                          const int32_t* block_table, int table_stride, const int32_t* row_slot,
                          const int32_t* query_start, const int32_t* kv_len, int rows, int heads, int kv_heads,
-                         int head_dim, int pages, int page_size, float scale, int window, int splits, cudaStream_t s) {
+                         int head_dim, int pages, int page_size, float scale, int window, int splits, const float* sinks,
+                         cudaStream_t s) {
     auto kernel = decode_kernel<D_PAD, STAGES>;
     const size_t smem = decode_smem<D_PAD>(STAGES);
     HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -531,10 +535,10 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
     dim3 grid(rows, kv_heads * m_tiles, splits);
     kernel<<<grid, 128, smem, s>>>(out, part_o, part_ml, q, kv, block_table, table_stride, row_slot, query_start,
                                    kv_len, heads, kv_heads, head_dim, pages, page_size, log2_exact(page_size),
-                                   scale * 1.4426950408889634f, window, splits);
+                                   scale * 1.4426950408889634f, window, splits, sinks);
     HB_LAUNCH_CHECK("attention_decode");
     if (splits > 1) {
-        decode_merge_kernel<<<dim3(rows, heads), 128, 0, s>>>(out, part_o, part_ml, query_start, heads, head_dim, splits);
+        decode_merge_kernel<<<dim3(rows, heads), 128, 0, s>>>(out, part_o, part_ml, query_start, heads, head_dim, splits, sinks);
         HB_LAUNCH_CHECK("attention_decode_merge");
     }
     return 0;
@@ -635,7 +639,7 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
                                         const int32_t* block_table, int table_stride, const int32_t* row_slot,
                                         const int32_t* query_start, const int32_t* kv_len, int rows, int heads,
                                         int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
-                                        int splits, hb_stream stream) {
+                                        int splits, const float* sinks, hb_stream stream) {
     if (rows == 0) return 0;
     if (head_dim % 16 || head_dim > 256 || head_dim < 16)
         HB_REFUSE("attention_decode_bf16: head_dim %d is no multiple of 16 up to 256", head_dim);
@@ -648,7 +652,7 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
     float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_ARGS (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, \
-    query_start, kv_len, rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, s
+    query_start, kv_len, rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, sinks, s
     if (head_dim <= 64) return launch_decode<64, 4>(HB_ARGS);
     if (head_dim <= 128) return launch_decode<128, 2>(HB_ARGS);   // two stages: three CTAs fit an SM, which hides latency better than a third stage
     return launch_decode<256, 2>(HB_ARGS);
@@ -846,7 +850,8 @@ __global__ void __launch_bounds__(128, (D_PAD <= 128 ? 3 : 1)) prefill_kernel(
         bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
-        int kv_heads, int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window) {
+        int kv_heads, int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window,
+        const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr uint32_t TILE_BYTES = TILE_N * D_PAD * 2;
     constexpr bool Q_IN_REGS = D_PAD <= 128;       // the queries then pass through the second stage's key tile
@@ -964,6 +969,11 @@ __global__ void __launch_bounds__(128, (D_PAD <= 128 ? 3 : 1)) prefill_kernel(
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sinks) {                                                    // the sink: a weight in the denominator that has no value
+        const float sk = sinks[h] * 1.4426950408889634f;
+        if (l0 > 0.f) l0 += ex2(fmaf(-m0, scale_log2, sk));
+        if (l1 > 0.f) l1 += ex2(fmaf(-m1, scale_log2, sk));
+    }
     const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
     const int r0 = warp * 16 + (lane >> 2), cq = (lane & 3) * 2;
 #pragma unroll
@@ -979,14 +989,14 @@ template <int D_PAD>
 static int launch_prefill(bf16* out, const bf16* q, const bf16* kv, const int32_t* block_table, int table_stride,
                           const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
                           int rows, int q_tiles, int heads, int kv_heads, int head_dim, int pages, int page_size,
-                          float scale, int window, cudaStream_t s) {
+                          float scale, int window, const float* sinks, cudaStream_t s) {
     auto kernel = prefill_kernel<D_PAD>;
     const size_t smem = (size_t)(4 * TILE_N + (D_PAD <= 128 ? 0 : 64)) * D_PAD * sizeof(bf16);
     HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (q_tiles > 65535) HB_REFUSE("attention_prefill: %d query tiles in one step, above 65535", q_tiles);
     kernel<<<dim3(heads, q_tiles), 128, smem, s>>>(out, q, kv, block_table, table_stride, row_slot, query_start,
                                                    kv_len, row0, rows, heads, kv_heads, head_dim, pages, page_size,
-                                                   log2_exact(page_size), scale * 1.4426950408889634f, window);
+                                                   log2_exact(page_size), scale * 1.4426950408889634f, window, sinks);
     HB_LAUNCH_CHECK("attention_prefill");
     return 0;
 }
@@ -996,7 +1006,7 @@ extern "C" int hb_attention_prefill_bf16(void* out, const void* q, const void* k
                                          int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                          const int32_t* kv_len, int row0, int rows, int q_tiles, int heads,
                                          int kv_heads, int head_dim, int pages, int page_size, float scale,
-                                         int window, hb_stream stream) {
+                                         int window, const float* sinks, hb_stream stream) {
     if (rows <= row0 || q_tiles == 0) return 0;
     if (head_dim % 16 || head_dim > 256 || head_dim < 16)
         HB_REFUSE("attention_prefill_bf16: head_dim %d is no multiple of 16 up to 256", head_dim);
@@ -1005,7 +1015,7 @@ extern "C" int hb_attention_prefill_bf16(void* out, const void* q, const void* k
     if (!(scale > 0.f)) HB_REFUSE("attention_prefill_bf16: the score scale must be positive");
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_ARGS (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len, \
-    row0, rows, q_tiles, heads, kv_heads, head_dim, pages, page_size, scale, window, s
+    row0, rows, q_tiles, heads, kv_heads, head_dim, pages, page_size, scale, window, sinks, s
     if (head_dim <= 64) return launch_prefill<64>(HB_ARGS);
     if (head_dim <= 128) return launch_prefill<128>(HB_ARGS);
     return launch_prefill<256>(HB_ARGS);

@@ -50,5 +50,5 @@ extern "C" int hb_attention_decode_bf16_static(void* out, const void* q, const v
         if (rc) return rc;
     }
     return hb_attention_decode_bf16(out, scratch, q, kv, block_table, table_stride, row_slot, query_start, kv_len,
-                                    rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, stream);
+                                    rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, nullptr, stream);
 }

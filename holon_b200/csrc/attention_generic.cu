@@ -13,7 +13,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
                                          const int32_t* __restrict__ kv_len, int rows, int tokens, int heads,
                                          int kv_heads, int head_dim, int pages, int page_size, float scale,
-                                         int window) {
+                                         int window, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long item = (long)blockIdx.x * GEN_WARPS + warp;
@@ -82,6 +82,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
             }
         }
     }
+    if (sinks && l > 0.f) l += expf(sinks[h] - m);        // the sink: a weight in the denominator that has no value
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < GEN_MAX_PER_LANE; ++i) {
@@ -94,7 +95,7 @@ extern "C" int hb_attention_generic(void* out, const void* q, const void* kv, in
                                     int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                     const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads,
                                     int head_dim, int pages, int page_size, float scale, int window,
-                                    hb_stream stream) {
+                                    const float* sinks, hb_stream stream) {
     if (tokens == 0 || rows == 0) return 0;
     if (head_dim > 32 * GEN_MAX_PER_LANE) HB_REFUSE("attention: head_dim %d is above %d", head_dim, 32 * GEN_MAX_PER_LANE);
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention: %d heads are no multiple of %d kv heads", heads, kv_heads);
@@ -105,11 +106,11 @@ extern "C" int hb_attention_generic(void* out, const void* q, const void* kv, in
     if (dtype == HB_F32)
         attention_generic_kernel<float><<<blocks, GEN_WARPS * 32, smem, s>>>(
             (float*)out, (const float*)q, (const float*)kv, block_table, table_stride, row_slot, query_start, kv_len,
-            rows, tokens, heads, kv_heads, head_dim, pages, page_size, scale, window);
+            rows, tokens, heads, kv_heads, head_dim, pages, page_size, scale, window, sinks);
     else if (dtype == HB_BF16)
         attention_generic_kernel<bf16><<<blocks, GEN_WARPS * 32, smem, s>>>(
             (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len,
-            rows, tokens, heads, kv_heads, head_dim, pages, page_size, scale, window);
+            rows, tokens, heads, kv_heads, head_dim, pages, page_size, scale, window, sinks);
     else HB_REFUSE("attention: dtype %d", dtype);
     HB_LAUNCH_CHECK("attention_generic");
     return 0;

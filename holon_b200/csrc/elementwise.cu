@@ -247,3 +247,125 @@ extern "C" int hb_silu_mul(void* out, const void* gate_up, int dtype, int tokens
     HB_LAUNCH_CHECK("silu_mul");
     return 0;
 }
+
+// ---------------------------------------------------------------- embedding with a scale and a table of token pairs
+// out[t] = table[id] * scale + pair[r], r = (previous id * mul_prev + id * mul_cur) mod buckets, or `buckets` (the pair
+// table's last row) for a sequence's first token (position 0). The previous id is the step's token before, or, for a
+// row's first token in this step, what `prev` [slots] holds for the row's slot; the block of a row's first token then
+// stores the row's last id there for the next step (it alone reads and writes that cell in this launch).
+template <typename T>
+__global__ void embed_pair_kernel(float* __restrict__ out, const T* __restrict__ table, float scale,
+                                  const T* __restrict__ pair, const int32_t* __restrict__ ids,
+                                  const int32_t* __restrict__ positions, const int32_t* __restrict__ query_start,
+                                  const int32_t* __restrict__ row_slot, int32_t* __restrict__ prev, int rows, int hidden,
+                                  int vocab, long mul_prev, long mul_cur, int buckets) {
+    const int t = blockIdx.x;
+    __shared__ int s_before;
+    if (threadIdx.x == 0) {
+        int lo = 0, hi = rows;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (query_start[mid] <= t) lo = mid; else hi = mid;
+        }
+        int before;
+        if (t > query_start[lo]) before = ids[t - 1];
+        else {
+            before = prev[row_slot[lo]];
+            prev[row_slot[lo]] = ids[query_start[lo + 1] - 1];
+        }
+        s_before = before;
+    }
+    __syncthreads();
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* row = table + (size_t)(ok ? id : 0) * hidden;
+    const T* extra = nullptr;
+    if (pair && ok) {
+        long r = buckets;
+        if (positions[t] > 0) {
+            r = ((long)s_before * mul_prev + (long)id * mul_cur) % buckets;
+            if (r < 0) r += buckets;
+        }
+        extra = pair + (size_t)r * hidden;
+    }
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        o[i] = ok ? to_f32(row[i]) * scale + (extra ? to_f32(extra[i]) : 0.f) : 0.f;
+}
+
+extern "C" int hb_embed_pair(float* out, const void* table, int table_dtype, float scale, const void* pair,
+                             const int32_t* ids, const int32_t* positions, const int32_t* query_start,
+                             const int32_t* row_slot, int32_t* prev, int rows, int tokens, int hidden, int vocab,
+                             long mul_prev, long mul_cur, int buckets, hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (pair && (buckets < 1 || !prev)) HB_REFUSE("embed_pair: a pair table needs buckets >= 1 and the slots' previous ids");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 1024 ? 256 : 128;
+#define HB_ARGS(T) out, (const T*)table, scale, (const T*)pair, ids, positions, query_start, row_slot, prev, rows, hidden, \
+    vocab, mul_prev, mul_cur, buckets
+    if (table_dtype == HB_F32) embed_pair_kernel<float><<<tokens, threads, 0, s>>>(HB_ARGS(float));
+    else if (table_dtype == HB_BF16) embed_pair_kernel<bf16><<<tokens, threads, 0, s>>>(HB_ARGS(bf16));
+    else HB_REFUSE("embed_pair: table dtype %d", table_dtype);
+#undef HB_ARGS
+    HB_LAUNCH_CHECK("embed_pair");
+    return 0;
+}
+
+// ---------------------------------------------------------------- the residual sum of a block whose parts run side by side
+// h[t, :] += sum_i scale_i x_i[t, :] + bias, in 32-bit; up to four terms of the engine's dtype, bias [hidden] or null.
+template <typename T>
+__global__ void sum_into_kernel(float* __restrict__ h, const T* __restrict__ x0, const T* __restrict__ x1,
+                                const T* __restrict__ x2, const T* __restrict__ x3, float s0, float s1, float s2, float s3,
+                                const T* __restrict__ bias, long count, int hidden) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float a = h[i];
+    if (x0) a = fmaf(s0, to_f32(x0[i]), a);
+    if (x1) a = fmaf(s1, to_f32(x1[i]), a);
+    if (x2) a = fmaf(s2, to_f32(x2[i]), a);
+    if (x3) a = fmaf(s3, to_f32(x3[i]), a);
+    if (bias) a += to_f32(bias[i % hidden]);
+    h[i] = a;
+}
+
+extern "C" int hb_sum_into(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1,
+                           float s2, float s3, const void* bias, int dtype, int tokens, int hidden, hb_stream stream) {
+    const long count = (long)tokens * hidden;
+    if (count == 0) return 0;
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) sum_into_kernel<float><<<blocks, 256, 0, s>>>(h, (const float*)x0, (const float*)x1, (const float*)x2, (const float*)x3, s0, s1, s2, s3, (const float*)bias, count, hidden);
+    else if (dtype == HB_BF16) sum_into_kernel<bf16><<<blocks, 256, 0, s>>>(h, (const bf16*)x0, (const bf16*)x1, (const bf16*)x2, (const bf16*)x3, s0, s1, s2, s3, (const bf16*)bias, count, hidden);
+    else HB_REFUSE("sum_into: dtype %d", dtype);
+    HB_LAUNCH_CHECK("sum_into");
+    return 0;
+}
+
+// ---------------------------------------------------------------- a gated unit with clamped inputs
+// gate_up [tokens, 2 inter] (gate columns first), bias [2 inter] or null: g = min(gate + b, limit),
+// u = clamp(up + b, -limit, limit), out = g sigmoid(alpha g) (u + 1), in 32-bit with one rounding.
+template <typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gate_up, const T* __restrict__ bias,
+                                   float limit, float alpha, int inter) {
+    const size_t t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    float g = to_f32(gate_up[t * 2 * inter + i]), u = to_f32(gate_up[t * 2 * inter + inter + i]);
+    if (bias) { g += to_f32(bias[i]); u += to_f32(bias[inter + i]); }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[t * inter + i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+extern "C" int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, float limit, float alpha,
+                              int tokens, int inter, hb_stream stream) {
+    if (tokens == 0 || inter == 0) return 0;
+    if (tokens > 65535) HB_REFUSE("glu_clamped: %d rows are above 65535", tokens);
+    dim3 grid((inter + 255) / 256, tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) glu_clamped_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)gate_up, (const float*)bias, limit, alpha, inter);
+    else if (dtype == HB_BF16) glu_clamped_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, (const bf16*)bias, limit, alpha, inter);
+    else HB_REFUSE("glu_clamped: dtype %d", dtype);
+    HB_LAUNCH_CHECK("glu_clamped");
+    return 0;
+}

@@ -61,6 +61,10 @@ class StepContext:
         self.from_last = None        # int32 [rows]: 1 where the row's token is fed from the device
         self.offset_of: dict = {}    # host: entry index -> offset of its first token among the step's tokens
 
+    def entry_slots(self, entry: int) -> dict:
+        """The fixed-size per-request tensors kept under cache entry `entry`, by name."""
+        return {name: t for (e, name), t in self._cache.slot_states.items() if e == entry}
+
     def layer_cache(self, run) -> LayerCache:
         c = self._cache
         group = c.group_of_entry.get(run.cache)

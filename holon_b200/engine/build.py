@@ -116,6 +116,8 @@ def build(source, *, dtype: str, device, kernels=None, page_size: int, max_seqs:
     tdtype = TORCH_DTYPES[dtype]
     raw = source.config()
     arch = resolve_architecture(raw)
+    if arch.complete is not None and hasattr(source, "shapes"):
+        raw = arch.complete(raw, source.shapes())
     config = arch.parse(raw)
     spec = arch.recipe(config)
     ctx = BuildContext(device, tdtype, kernels, max_positions=max_model_len, max_step_tokens=max_step_tokens)

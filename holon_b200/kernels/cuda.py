@@ -408,15 +408,20 @@ class CudaKernels:
                    ctypes.c_float(scaled.eps if scaled else 0.0), scaled.dim if scaled else 0)
         return True
 
-    def paged_attention(self, out, q, kv, block_table, rows, scale, window) -> None:
-        self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len)
+    def paged_attention(self, out, q, kv, block_table, rows, scale, window, sinks=None) -> None:
+        """`sinks` (float32 [heads], or None): a weight exp(sinks[h]) in each head's softmax denominator that has
+        neither key nor value. Rows of one token then take the split kernel with its merge kernel (the cluster and the
+        balanced forms do not know sinks), rows of several the mma.sync kernel."""
+        self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len, sinks)
         t, heads, head_dim = q.shape
+        if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (heads,)):
+            raise KernelError("paged_attention: sinks must be float32 [heads]")
         if out.shape != q.shape or kv.dtype != q.dtype or out.dtype != q.dtype or kv.shape[4] != head_dim:
             raise KernelError("paged_attention: out and q [tokens, heads, head_dim], kv [pages, 2, kv_heads, page_size, "
                               "head_dim], one dtype")
         fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and self.attention_bf16 == "fast"
         if not fast:
-            return self._attention_generic(out, q, kv, block_table, rows, scale, window)
+            return self._attention_generic(out, q, kv, block_table, rows, scale, window, sinks)
         kv_heads = kv.shape[2]
         common = (self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
                   self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"))
@@ -424,7 +429,7 @@ class CudaKernels:
         if rows.n_decode:
             splits = self.decode_splits(rows.n_decode, heads, kv_heads, rows.max_kv)
             mode = self._decode_mode_of(rows)
-            if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
+            if sinks is None and splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
                 pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
                 slots = self.sms * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
                 if 2 * pairs <= slots:                                # a whole number of CTAs per (row, kv head): rows of
@@ -436,7 +441,7 @@ class CudaKernels:
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
                 self._call("hb_attention_decode_bf16_balanced", self._p(out), self._p(scratch), self._p(q), self._p(kv),
                            *common, rows.n_decode, *sizes, ctas)
-            elif splits > 1 and (few := self.decode_cluster_splits(rows.n_decode, heads, kv_heads, head_dim,
+            elif sinks is None and splits > 1 and (few := self.decode_cluster_splits(rows.n_decode, heads, kv_heads, head_dim,
                                                                    rows.max_kv, splits)):
                 self._call("hb_attention_decode_bf16_cluster", self._p(out), self._p(q), self._p(kv), *common,
                            rows.n_decode, *sizes, few)
@@ -444,9 +449,9 @@ class CudaKernels:
                 floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None
                 self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
-                           rows.n_decode, *sizes, splits)
+                           rows.n_decode, *sizes, splits, self._p(sinks))
         if rows.n_rows > rows.n_decode:
-            if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
+            if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0 and sinks is None:
                 tile_q, tiles = 256, self._query_tiles(rows, 256)
                 if self.prefill_tile == 128 or (self.prefill_tile is None and 4 * heads * tiles < 3 * self.sms):              # tiles of 256 queries would leave SMs idle: one group of
                     tile_q, tiles = 128, self._query_tiles(rows, 128)   # 128 a CTA, twice the CTAs
@@ -454,7 +459,7 @@ class CudaKernels:
                            rows.n_decode, rows.n_rows, tiles, t, *sizes, tile_q)
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
-                           rows.n_rows, self._query_tiles(rows, 64), *sizes)
+                           rows.n_rows, self._query_tiles(rows, 64), *sizes, self._p(sinks))
 
     KV_BUCKET_MIN = 512                       # the smallest number of keys a captured decode launch is planned for
 
@@ -559,12 +564,13 @@ class CudaKernels:
             self._splits[key] = int(fn(int(head_dim), int(splits)))
         return self._splits[key]
 
-    def _attention_generic(self, out, q, kv, block_table, rows, scale, window) -> None:
+    def _attention_generic(self, out, q, kv, block_table, rows, scale, window, sinks=None) -> None:
         t, heads, head_dim = q.shape
         self._call("hb_attention_generic", self._p(out), self._p(q), self._p(kv), _code(q),
                    self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
                    self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"), rows.n_rows, t,
-                   heads, kv.shape[2], head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
+                   heads, kv.shape[2], head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window),
+                   self._p(sinks))
 
     # ---- the residual sum and the next norm inside the product that ends a part (decode steps)
     def can_link(self, rows: int, hidden: int, norm) -> bool:
@@ -928,6 +934,117 @@ class CudaKernels:
             raise KernelError("expert_combine: y [tokens * top, hidden], shared [tokens, hidden], z float32 [tokens, > experts]")
         self._call("hb_expert_combine", self._p(out), self._p(y), _code(out), self._i32(place, "place"), self._p(weight),
                    self._p(shared), self._p(z), z.shape[1] if z is not None else 0, int(experts), t, top, hidden)
+
+    # ---- a block whose parts run side by side, an embedding with a pair table, mixers with a matrix state per head
+    def embed_pair(self, out, table, scale, pair, ids, positions, rows, prev, mul_prev, mul_cur, buckets) -> None:
+        """out = table[ids] · scale + pair[row of (previous id, id)] (csrc/api.h: hb_embed_pair); `prev` int32 [slots]."""
+        self._check(out, table, pair, ids, positions, rows.query_start, rows.row_slot, prev)
+        if out.dtype != torch.float32 or out.shape != (ids.shape[0], table.shape[1]):
+            raise KernelError("embed_pair: out must be float32 [tokens, hidden]")
+        if pair is not None and (pair.dtype != table.dtype or pair.shape != (buckets + 1, table.shape[1])):
+            raise KernelError("embed_pair: the pair table must be [buckets + 1, hidden] of the table's dtype")
+        self._call("hb_embed_pair", self._p(out), self._p(table), _code(table), ctypes.c_float(scale), self._p(pair),
+                   self._i32(ids, "ids"), self._i32(positions, "positions"), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.row_slot, "row_slot"), self._i32(prev, "prev"), rows.n_rows, ids.shape[0],
+                   table.shape[1], table.shape[0], ctypes.c_long(mul_prev), ctypes.c_long(mul_cur), int(buckets))
+
+    def sum_into(self, h, terms, bias=None) -> None:
+        """h (float32 [tokens, hidden]) += Σ scale · x over `terms` [(x, scale), ...] (up to four) + bias."""
+        xs = [x for x, _ in terms]
+        self._check(h, bias, *xs)
+        if not 1 <= len(terms) <= 4 or h.dtype != torch.float32 or any(x.shape != h.shape or x.dtype != xs[0].dtype for x in xs):
+            raise KernelError("sum_into: one to four terms of h's shape and one dtype, h float32")
+        if bias is not None and (bias.shape != (h.shape[1],) or bias.dtype != xs[0].dtype):
+            raise KernelError("sum_into: bias must be [hidden] of the terms' dtype")
+        xs += [None] * (4 - len(xs))
+        scales = [float(sc) for _, sc in terms] + [0.0] * (4 - len(terms))
+        self._call("hb_sum_into", self._p(h), *(self._p(x) for x in xs), *(ctypes.c_float(sc) for sc in scales),
+                   self._p(bias), _code(terms[0][0]), h.shape[0], h.shape[1])
+
+    def glu_clamped(self, out, gate_up, bias, limit, alpha) -> None:
+        self._check(out, gate_up, bias)
+        if gate_up.shape != (out.shape[0], 2 * out.shape[1]) or out.dtype != gate_up.dtype \
+                or (bias is not None and (bias.shape != (gate_up.shape[1],) or bias.dtype != out.dtype)):
+            raise KernelError("glu_clamped: gate_up [tokens, 2 inter] and bias [2 inter] of out's dtype")
+        self._call("hb_glu_clamped", self._p(out), self._p(gate_up), self._p(bias), _code(out), ctypes.c_float(limit),
+                   ctypes.c_float(alpha), out.shape[0], out.shape[1])
+
+    @staticmethod
+    def _f32(what: str, *tensors) -> None:
+        for t in tensors:
+            if t is not None and t.dtype != torch.float32:
+                raise KernelError(f"{what}: 32-bit tensors expected, got {t.dtype}")
+
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows) -> None:
+        """The token-by-token update of a matrix state per head (csrc/api.h: hb_recurrent_scan)."""
+        self._check(out, qk, v, decay, head_decay, beta, state, rows.query_start, rows.row_slot)
+        self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state)
+        t, heads, vdim = v.shape
+        kv_heads, dim = qk.shape[2], qk.shape[3]
+        if qk.shape != (t, 2, kv_heads, dim) or out.shape != v.shape or state.shape[1:] != (heads, dim, vdim) \
+                or (decay is not None and decay.shape != (t, heads, dim)) or (beta is not None and beta.shape != (t, heads)) \
+                or (head_decay is not None and head_decay.shape != (heads,)):
+            raise KernelError("recurrent_scan: qk [tokens, 2, kv_heads, dim], v and out [tokens, heads, vdim], state "
+                              "[slots, heads, dim, vdim], decay [tokens, heads, dim] or head_decay [heads], beta [tokens, heads]")
+        self._call("hb_recurrent_scan", self._p(out), self._p(qk), self._p(v), self._p(decay), self._p(head_decay),
+                   self._p(beta), self._p(state), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, heads, kv_heads, dim, vdim)
+
+    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows, q_scale,
+                      unit_eps) -> None:
+        """From a delta-rule mixer's first product to the scan's inputs (csrc/api.h: hb_delta_prepare)."""
+        self._check(qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows.query_start, rows.row_slot)
+        self._f32("delta_prepare", qk, v, beta, decay, gate, dt_bias, rate_log)
+        t, heads, vdim = v.shape
+        kv_heads, dim = qk.shape[2], qk.shape[3]
+        ra, rg, taps = a2.shape[1], g2.shape[1], conv.shape[1]
+        channels = 2 * kv_heads * dim + heads * vdim
+        if first.shape != (t, channels + heads + ra + rg) or conv.shape[0] != channels or a2.shape[0] != heads * dim \
+                or g2.shape[0] != heads * vdim or any(x.dtype != first.dtype for x in (conv, a2, g2)) \
+                or (taps > 1 and (conv_state is None or conv_state.shape[1:] != (taps - 1, channels) or conv_state.dtype != first.dtype)):
+            raise KernelError("delta_prepare: first [tokens, q | k | v | b | a1 | g1], conv [channels, taps], conv_state "
+                              "[slots, taps - 1, channels], a2 [heads dim, ra], g2 [heads vdim, rg], of one dtype")
+        self._call("hb_delta_prepare", self._p(qk), self._p(v), self._p(beta), self._p(decay), self._p(gate),
+                   self._p(first), _code(first), first.shape[1], self._p(conv), taps, self._p(conv_state), self._p(a2),
+                   self._p(dt_bias), self._p(rate_log), self._p(g2), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, t, heads, kv_heads, dim, vdim, ra, rg,
+                   ctypes.c_float(q_scale), ctypes.c_float(unit_eps))
+
+    def conv_carry(self, conv_state, first, channels, taps, rows) -> None:
+        if taps <= 1:
+            return
+        self._check(conv_state, first, rows.query_start, rows.row_slot)
+        self._call("hb_conv_carry", self._p(conv_state), self._p(first), _code(first), first.shape[1], channels, taps,
+                   self._i32(rows.query_start, "query_start"), self._i32(rows.row_slot, "row_slot"), rows.n_rows)
+
+    def retention_prepare(self, qk, v, first, positions, table, rot_dims, k_scale) -> None:
+        self._check(qk, v, first, positions, table)
+        self._f32("retention_prepare", qk, v, table)
+        t, heads, vdim = v.shape
+        dim = qk.shape[3]
+        if qk.shape != (t, 2, heads, dim) or first.shape[0] != t or first.shape[1] < 2 * heads * dim + heads * vdim \
+                or (rot_dims and (table is None or table.shape[1] != rot_dims)):
+            raise KernelError("retention_prepare: qk [tokens, 2, heads, dim], v [tokens, heads, vdim], first [tokens, q | k | v | ...]")
+        self._call("hb_retention_prepare", self._p(qk), self._p(v), self._p(first), _code(first), first.shape[1],
+                   self._i32(positions, "positions"), self._p(table), int(rot_dims),
+                   table.shape[0] if table is not None else 0, t, heads, dim, vdim, ctypes.c_float(k_scale))
+
+    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps) -> None:
+        """out = o / rms(o) · weight · gate per head; `gate_pre` may be a view into wider rows (silu of it is the gate)."""
+        self._check(out, o, weight, gate_mul)
+        self._f32("head_norm_gate", o, weight, gate_mul)
+        t, heads, vdim = o.shape
+        ld = 0
+        if gate_pre is not None:
+            if gate_pre.shape != (t, heads * vdim) or gate_pre.dtype != out.dtype or gate_pre.stride(1) != 1 \
+                    or gate_pre.get_device() != self._index:
+                raise KernelError("head_norm_gate: gate_pre must be [tokens, heads vdim] of out's dtype, innermost stride 1")
+            ld = gate_pre.stride(0)
+        if out.shape != o.shape or (weight is not None and weight.shape != (vdim,)) \
+                or (gate_mul is not None and gate_mul.numel() != o.numel()):
+            raise KernelError("head_norm_gate: out and o [tokens, heads, vdim], weight [vdim], gate_mul of o's size")
+        self._call("hb_head_norm_gate", self._p(out), self._p(o), _code(out), self._p(weight), self._p(gate_mul),
+                   self._p(gate_pre), ctypes.c_long(ld), ctypes.c_float(eps), t, heads, vdim)
 
     def feed_tokens(self, token_ids, last_tokens, rows, from_last) -> None:
         """token_ids[first token of row r] = last_tokens[slot of row r] for the rows whose `from_last` is set."""

@@ -2,13 +2,15 @@
 from .attention import GQA
 from .base import register_part
 from .block import PreNorm
-from .embedding import Embedding, Head
+from .embedding import Embedding, Head, PairEmbedding
 from .experts import Experts
-from .feedforward import SwiGLU
+from .feedforward import ClampedGLU, SwiGLU
 from .hyper import Hyper
 from .latent import LatentAttention
 from .norm import RMSNorm
+from .parallel import ParallelBlock, SideBySide
 from .position import Rope
+from .recurrent import GatedDelta, Retention
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 register_part("position", "rope", Rope, replace=True)
@@ -20,3 +22,9 @@ register_part("block", "prenorm", PreNorm, replace=True)
 register_part("block", "hyper", Hyper, replace=True)
 register_part("embed", "table", Embedding, replace=True)
 register_part("head", "linear", Head, replace=True)
+register_part("mixer", "retention", Retention, replace=True)
+register_part("mixer", "gated_delta", GatedDelta, replace=True)
+register_part("mixer", "side_by_side", SideBySide, replace=True)
+register_part("ffn", "clamped_glu", ClampedGLU, replace=True)
+register_part("block", "parallel", ParallelBlock, replace=True)
+register_part("embed", "pair", PairEmbedding, replace=True)

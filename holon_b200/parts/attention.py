@@ -5,6 +5,14 @@ step's pages, attention of the new rows over everything the request holds, outpu
 (std/holon_std/mixers/gqa/units.py:108-294; formulas std/holon_std/mixers/gqa/reference.py:26-60, 91-101).
 Query head h reads KV head h // (heads / kv_heads); a query at position p sees keys j ≤ p, and with a window W > 0
 only those with p − j < W.
+
+Options that other designs use, each a constructor argument: `scale` (the score scale, 1/√head_dim unless given);
+`unit_norm_eps` (q and k are divided by their root mean square per head, a norm without a weight, in place of
+`qk_norm`); `values_are_keys` (there is no value projection: a token's value is its key as projected, before any norm;
+the merged product then has the key's rows twice, so that the cache write stores the normed copy as the key and the
+plain copy as the value); `sink` (one learned number per head, stored as `sink`: exp(sink) stands in the softmax's
+denominator, without key or value and without the score scale); `names` (the stored names of the q, k, v and output
+weights, where they are not `q_proj.weight` and so on).
 """
 from __future__ import annotations
 
@@ -17,16 +25,27 @@ from .linear import Linear
 
 class GQA(Part):
     def __init__(self, ctx: BuildContext, *, heads: int, kv_heads: int, head_dim: int, hidden: int,
-                 position: PartRef | None, qk_norm: PartRef | None = None, window: int = 0, layer: int = 0) -> None:
+                 position: PartRef | None, qk_norm: PartRef | None = None, window: int = 0, layer: int = 0,
+                 scale: float | None = None, unit_norm_eps: float | None = None, values_are_keys: bool = False,
+                 sink: bool = False, names: tuple[tuple[str, str], ...] = ()) -> None:
         super().__init__()
         if heads % kv_heads:
             raise ValueError(f"gqa: {heads} heads are no multiple of {kv_heads} kv heads")
+        if qk_norm is not None and unit_norm_eps is not None:
+            raise ValueError("gqa: give qk_norm or unit_norm_eps, not both")
         self.ctx, self.heads, self.kv_heads, self.head_dim, self.window = ctx, heads, kv_heads, head_dim, int(window)
-        self.scale = 1.0 / head_dim ** 0.5
-        self.qkv = self.add_child("qkv", Linear(ctx, "weight", hidden, {
-            "q_proj.weight": heads * head_dim, "k_proj.weight": kv_heads * head_dim,
-            "v_proj.weight": kv_heads * head_dim}))
+        self.scale = 1.0 / head_dim ** 0.5 if scale is None else float(scale)
+        self.unit_norm_eps, self.values_are_keys = unit_norm_eps, bool(values_are_keys)
+        self._names = {"q_proj.weight": "q_proj.weight", "k_proj.weight": "k_proj.weight",
+                       "v_proj.weight": "v_proj.weight", "o_proj.weight": "o_proj.weight", **dict(names)}
+        pieces = {"q_proj.weight": heads * head_dim, "k_proj.weight": kv_heads * head_dim}
+        if not values_are_keys:
+            pieces["v_proj.weight"] = kv_heads * head_dim
+        self.qkv = self.add_child("qkv", Linear(ctx, "weight", hidden, pieces,
+                                                spare=kv_heads * head_dim if values_are_keys else 0))
         self.o_proj = self.add_child("o_proj", Linear(ctx, "weight", heads * head_dim, {"weight": hidden}))
+        self.sink = self.add_param("sink", (heads,), "coef") if sink else None
+        self._unit = None                    # the gain of a norm without a weight: ones (made in finalize)
         self.q_norm = self.k_norm = None
         if qk_norm is not None:
             self.q_norm = self.add_child("q_norm", ctx.part(qk_norm, dim=head_dim))
@@ -36,7 +55,18 @@ class GQA(Part):
     # the loadable names of the merged product are the stored ones, without the child's own prefix
     def loadables(self, prefix: str = ""):
         for name, p, rows in super().loadables(prefix):
-            yield name.replace(prefix + "qkv.", prefix, 1), p, rows
+            name = name.replace(prefix + "qkv.", prefix, 1)
+            yield prefix + self._names.get(name[len(prefix):], name[len(prefix):]), p, rows
+
+    def finalize(self) -> None:
+        super().finalize()
+        w = self.qkv.weight.tensor
+        if w is not None:
+            if self.values_are_keys:                                 # the value rows: the key's, a second time
+                n, at = self.kv_heads * self.head_dim, self.heads * self.head_dim
+                w[at + n:at + 2 * n].copy_(w[at:at + n])
+            if self.unit_norm_eps is not None:
+                self._unit = torch.ones(self.head_dim, dtype=w.dtype, device=w.device)
 
     takes_scaled = True                      # x may be base.Scaled: both first products apply the row scale
 
@@ -60,14 +90,18 @@ class GQA(Part):
         t, k = x.shape[0], self.ctx.kernels
         q = self.ctx.empty(t, self.heads, self.head_dim)
         norm, pos = self.q_norm, self.position
+        q_gain, k_gain = (norm.weight.tensor, self.k_norm.weight.tensor) if norm else (self._unit, self._unit)
+        eps = norm.eps if norm else (self.unit_norm_eps or 0.0)
         after = (step.positions, pos.table if pos else None, pos.rotary_dim if pos else 0,
-                 norm.weight.tensor if norm else None, self.k_norm.weight.tensor if norm else None,
-                 norm.eps if norm else 0.0, norm.offset if norm else 0.0,
+                 q_gain, k_gain, eps, norm.offset if norm else 0.0,
                  cache.kv if cache.fills else None, cache.group.write_index if cache.fills else None,
                  self.heads, self.kv_heads, self.head_dim)
         fused = getattr(k, "qkv_rope", None)                         # a kernel table may do the product and what follows in one
         if fused is None or not fused(q, x, self.qkv.weight.tensor, *after):
             k.qk_norm_rope_kv_write(q, self.qkv.forward(x), *after)
         o = self.ctx.empty(t, self.heads, self.head_dim)
-        k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window)
+        if self.sink is not None:
+            k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window, self.sink.tensor)
+        else:
+            k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window)
         return self.o_proj.forward(o.view(t, self.heads * self.head_dim), link=take_link(step))

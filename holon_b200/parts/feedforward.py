@@ -1,5 +1,8 @@
 """SwiGLU: down(silu(gate(x)) · up(x)), gate and up in one product with gate's rows first, silu in 32-bit
-(std/holon_std/ffn/units.py:12-50; std/holon_std/ffn/reference.py:7-12)."""
+(std/holon_std/ffn/units.py:12-50; std/holon_std/ffn/reference.py:7-12).
+
+ClampedGLU: a gated unit whose inputs are clamped, with a bias on every projection: g = min(W_gate x + b, limit),
+u = clamp(W_up x + b, −limit, limit), y = g · sigmoid(alpha · g) · (u + 1), output W_down y + b."""
 from __future__ import annotations
 
 import torch
@@ -26,3 +29,33 @@ class SwiGLU(Part):
         act = self.ctx.empty(x.shape[0], self.inter)
         self.ctx.kernels.swiglu_gate_up(act, x, self.gate_up.weight.tensor)
         return self.down.forward(act, link=take_link(step))
+
+
+class ClampedGLU(Part):
+    def __init__(self, ctx: BuildContext, *, inter: int, hidden: int, limit: float, alpha: float = 1.702,
+                 layer: int = 0) -> None:
+        super().__init__()
+        self.ctx, self.inter, self.limit, self.alpha = ctx, inter, float(limit), float(alpha)
+        self.gate_up = self.add_child("gate_up_proj", Linear(ctx, "weight", hidden, {"gate": inter, "up": inter}))
+        self.first_bias = self.add_param("first_bias", (2 * inter,), "matrix", {"gate.b": (0, inter), "up.b": (inter, 2 * inter)})
+        self.down = self.add_child("down_proj", Linear(ctx, "weight", inter, {"down": hidden}))
+        self.down_bias = self.add_param("down.b", (hidden,), "matrix")
+
+    def loadables(self, prefix: str = ""):
+        for name, p, rows in super().loadables(prefix):
+            for child in ("gate_up_proj.", "down_proj."):
+                if name.startswith(prefix + child):
+                    name = prefix + name[len(prefix + child):]
+            yield name, p, rows
+
+    def forward_biased(self, x: torch.Tensor, step):
+        """(W_down y, its bias): a block that sums several parts adds the bias there."""
+        k = self.ctx.kernels
+        z = self.gate_up.forward(x)
+        act = self.ctx.empty(x.shape[0], self.inter)
+        k.glu_clamped(act, z, self.first_bias.tensor, self.limit, self.alpha)
+        return self.down.forward(act), self.down_bias.tensor
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        y, bias = self.forward_biased(x, step)
+        return y + bias

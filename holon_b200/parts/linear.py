@@ -8,15 +8,16 @@ from .base import BuildContext, Part
 
 
 class Linear(Part):
-    def __init__(self, ctx: BuildContext, name: str, width_in: int, pieces: dict[str, int]) -> None:
-        """`pieces`: loadable name -> rows, in the order they are stacked."""
+    def __init__(self, ctx: BuildContext, name: str, width_in: int, pieces: dict[str, int], spare: int = 0) -> None:
+        """`pieces`: loadable name -> rows, in the order they are stacked. `spare`: so many rows more behind them that
+        no stored tensor fills; the part that asked for them writes them in its `finalize()`."""
         super().__init__()
         self.ctx, self.width_in = ctx, width_in
         rows, at = {}, 0
         for piece, n in pieces.items():
             rows[piece], at = (at, at + n), at + n
-        self.width_out = at
-        self.weight = self.add_param(name, (at, width_in), "matrix", rows)
+        self.width_out = at + spare
+        self.weight = self.add_param(name, (at + spare, width_in), "matrix", rows)
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, link=None) -> torch.Tensor | None:
         """x · Wᵀ. With `link` (base.Link): the product is added into the link's stream, the rows of the link's norm

@@ -11,6 +11,9 @@ from ..config.spec import ModelSpec
 from .base import BuildContext, PagedKV, PagedLatent, Part, SlotState
 
 
+EMBED_ENTRY = -1          # the entry number under which the embedding's per-request state is kept
+
+
 @dataclasses.dataclass(frozen=True)
 class CacheEntry:
     """One cache entry of the run order: which layer fills it and what that layer's mixer asked for."""
@@ -39,6 +42,9 @@ class Model(Part):
         self.layers = []
         built: dict = {}
         for i, layer in enumerate(spec.layers):
+            if layer is None:                                 # (its runs use another layer's parts)
+                self.layers.append(None)
+                continue
             block = ctx.part(layer.block, layer=i, hidden=spec.hidden, mixer=layer.mixer, ffn=layer.ffn,
                              norm=layer.norm)
             self.layers.append(self.add_child(f"layers.{i}", block))
@@ -47,13 +53,16 @@ class Model(Part):
         self.entries = self._entries()
         planners: dict = {}                                   # one mixer of each kind that plans captured steps
         for layer in self.layers:
-            mixer = getattr(layer, "mixer", None)
+            mixer = getattr(layer, "mixer", None)              # (None for a layer without parts of its own)
             if hasattr(mixer, "capture_plan"):
                 planners.setdefault(getattr(mixer, "plan_group", id(mixer)), mixer)
         self._planners = tuple(planners.values())
 
     def _entries(self) -> tuple[CacheEntry, ...]:
         entries: dict[int, CacheEntry] = {}
+        carried = tuple(getattr(self.embed, "slot_states", tuple)())
+        if carried:                                           # what the embedding carries from step to step per request
+            entries[EMBED_ENTRY] = CacheEntry(EMBED_ENTRY, -1, None, carried)
         for run in self.spec.order:
             mixer = self.layers[run.layer].mixer
             decl, slots = mixer.cache(), tuple(mixer.slot_states())
@@ -76,7 +85,10 @@ class Model(Part):
 
     def trunk(self, step):
         """The residual stream after the last run, for every token of the step."""
-        stream = self.embed.forward(step.token_ids)
+        if getattr(self.embed, "wants_step", False):          # an embedding that reads positions, rows or carried state
+            stream = self.embed.forward(step.token_ids, step)
+        else:
+            stream = self.embed.forward(step.token_ids)
         order = self.spec.order
         for i, run in enumerate(order):
             after = self.layers[order[i + 1].layer] if i + 1 < len(order) else None

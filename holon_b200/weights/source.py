@@ -41,6 +41,16 @@ class SafetensorsSource:
                 ids += [eos] if isinstance(eos, int) else list(eos or ())
         return tuple(dict.fromkeys(ids))
 
+    def shapes(self) -> dict[str, tuple[int, ...]]:
+        """Stored name -> shape, from the files' headers alone."""
+        from safetensors import safe_open
+        out: dict[str, tuple[int, ...]] = {}
+        for path in self.files:
+            with safe_open(str(path), framework="pt") as f:
+                for name in f.keys():
+                    out[name] = tuple(f.get_slice(name).get_shape())
+        return out
+
     def tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
         from safetensors import safe_open
         seen: dict[str, pathlib.Path] = {}

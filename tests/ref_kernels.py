@@ -68,7 +68,7 @@ class RefKernels:
             kv[page, 0, :, off] = k[ok]
             kv[page, 1, :, off] = v[ok]
 
-    def paged_attention(self, out, q, kv, block_table, rows, scale, window):
+    def paged_attention(self, out, q, kv, block_table, rows, scale, window, sinks=None):
         page_size, hq, hkv = kv.shape[3], q.shape[1], kv.shape[2]
         out.zero_()
         qs, slots, lens = rows.query_start.tolist(), rows.row_slot.tolist(), rows.kv_len.tolist()
@@ -85,7 +85,10 @@ class RefKernels:
             hidden = key > pos
             if window > 0:
                 hidden = hidden | (pos - key >= window)
-            probs = scores.masked_fill(hidden, float("-inf")).softmax(-1)
+            scores = scores.masked_fill(hidden, float("-inf"))
+            if sinks is not None:                          # a weight in the denominator without key or value
+                scores = torch.cat((scores, sinks.float()[:, None, None].expand(-1, e - s, 1)), -1)
+            probs = scores.softmax(-1)[..., :n]
             out[s:e] = torch.einsum("hqk,khd->qhd", probs, v).to(out.dtype)
 
     def silu_mul(self, out, gate_up):
@@ -99,6 +102,103 @@ class RefKernels:
 
     def linear(self, out, x, weight):
         out.copy_((x.float() @ weight.float().T).to(out.dtype))
+
+    # ---- a block whose parts run side by side, an embedding with a pair table, mixers with a matrix state per head
+    def embed_pair(self, out, table, scale, pair, ids, positions, rows, prev, mul_prev, mul_cur, buckets):
+        ids_, pos = ids.tolist(), positions.tolist()
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        x = table[ids.long()].float() * scale
+        for b in range(rows.n_rows):
+            for t in range(qs[b], qs[b + 1]):
+                before = ids_[t - 1] if t > qs[b] else int(prev[slots[b]])
+                if pair is not None:
+                    r = buckets if pos[t] == 0 else (before * mul_prev + ids_[t] * mul_cur) % buckets
+                    x[t] += pair[r].float()
+            if prev is not None and qs[b + 1] > qs[b]:
+                prev[slots[b]] = ids_[qs[b + 1] - 1]
+        out.copy_(x)
+
+    def sum_into(self, h, terms, bias=None):
+        for x, scale in terms:
+            h += scale * x.float()
+        if bias is not None:
+            h += bias.float()
+
+    def glu_clamped(self, out, gate_up, bias, limit, alpha):
+        z = gate_up.float() + (bias.float() if bias is not None else 0.0)
+        g, u = z.chunk(2, dim=-1)
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
+
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows):
+        t, heads, vdim = v.shape
+        group = heads // qk.shape[2]
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        for b in range(rows.n_rows):
+            for h in range(heads):
+                s = state[slots[b], h].clone()
+                for i in range(qs[b], qs[b + 1]):
+                    q, k = qk[i, 0, h // group], qk[i, 1, h // group]
+                    s = s * (decay[i, h][:, None] if decay is not None else head_decay[h])
+                    u = v[i, h] if beta is None else beta[i, h] * (v[i, h] - s.T @ k)
+                    s = s + torch.outer(k, u)
+                    out[i, h] = s.T @ q
+                state[slots[b], h] = s
+
+    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows, q_scale,
+                      unit_eps):
+        t, heads, vdim = v.shape
+        kv_heads, dim = qk.shape[2], qk.shape[3]
+        taps, ra, rg = conv.shape[1], a2.shape[1], g2.shape[1]
+        nq, nv = kv_heads * dim, heads * vdim
+        c = 2 * nq + nv
+        x = first.float()
+        y = torch.zeros(t, c)
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        for b in range(rows.n_rows):
+            s, e = qs[b], qs[b + 1]
+            carried = conv_state[slots[b]].float() if taps > 1 else torch.zeros(0, c)
+            seq = torch.cat((carried, x[s:e, :c]), 0)
+            y[s:e] = sum(seq[j:j + e - s] * conv.float()[:, j] for j in range(taps))
+        y = y * torch.sigmoid(y)
+        unit = lambda z: z / torch.sqrt((z * z).sum(-1, keepdim=True) + unit_eps)      # noqa: E731
+        qk[:, 0] = unit(y[:, :nq].view(t, kv_heads, dim)) * q_scale
+        qk[:, 1] = unit(y[:, nq:2 * nq].view(t, kv_heads, dim))
+        v.copy_(y[:, 2 * nq:].view(t, heads, vdim))
+        beta.copy_(torch.sigmoid(x[:, c:c + heads]))
+        a = x[:, c + heads:c + heads + ra] @ a2.float().T + dt_bias
+        decay.copy_(torch.exp(-torch.exp(rate_log)[None, :, None] * torch.nn.functional.softplus(a).view(t, heads, dim)))
+        gate.copy_(torch.sigmoid(x[:, c + heads + ra:] @ g2.float().T).view(gate.shape))
+
+    def conv_carry(self, conv_state, first, channels, taps, rows):
+        if taps <= 1:
+            return
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        for b in range(rows.n_rows):
+            seq = torch.cat((conv_state[slots[b]], first[qs[b]:qs[b + 1], :channels]), 0)
+            conv_state[slots[b]] = seq[-(taps - 1):]
+
+    def retention_prepare(self, qk, v, first, positions, table, rot_dims, k_scale):
+        t, heads, vdim = v.shape
+        dim = qk.shape[3]
+        x = first.float()
+        for which in (0, 1):
+            z = x[:, which * heads * dim:(which + 1) * heads * dim].view(t, heads, dim)
+            if rot_dims:
+                z = self._turn(z, table[positions.long()][:, None, :], rot_dims)
+            qk[:, which] = z * (k_scale if which else 1.0)
+        v.copy_(x[:, 2 * heads * dim:2 * heads * dim + heads * vdim].view(t, heads, vdim))
+
+    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps):
+        y = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            y = y * weight
+        if gate_mul is not None:
+            y = y * gate_mul.view(o.shape)
+        elif gate_pre is not None:
+            g = gate_pre.float().view(o.shape)
+            y = y * g * torch.sigmoid(g)
+        out.copy_(y.to(out.dtype))
 
     def feed_tokens(self, token_ids, last_tokens, rows, from_last):
         for r in range(rows.n_rows):

@@ -61,7 +61,7 @@ def test_static_scratch_entry_point_matches_the_one_that_takes_scratch():
         assert 0 < floats <= capacity
         scratch = torch.empty(floats, dtype=torch.float32, device=DEV)
         want = torch.full_like(c["q"], float("nan"))
-        assert lib.hb_attention_decode_bf16(p(want), p(scratch), *common) == 0, lib.hb_last_error()
+        assert lib.hb_attention_decode_bf16(p(want), p(scratch), *common[:-1], ctypes.c_void_p(0), stream) == 0, lib.hb_last_error()
         got = torch.full_like(c["q"], float("nan"))
         assert lib.hb_attention_decode_bf16_static(p(got), *common) == 0, lib.hb_last_error()
         torch.cuda.synchronize()

@@ -84,6 +84,35 @@ RULORAX_SIZES = {
 }
 
 
+def kasovik_config(width: int, heads: int, kv_heads: int, dim: int, window: int, ff: int, layers: int, rank: int = 64,
+                   taps: int = 4, vocab: int = 32768) -> dict:
+    """A Kasovik model for `--only kasovik`: of every three layers two are parallel ones (windowed attention with a sink
+    beside a gated delta rule) and the third a retention layer, each with weights of its own."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "scale": dim ** -0.5}
+    right = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": taps, "decay_rank": rank, "gate_rank": rank}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp}
+    retention = {"type": "retention", "mlp": mlp,
+                 "mixer": {"heads": heads, "dim": dim, "vdim": dim, "decay": [1 - 2.0 ** (-5 - h % 6) for h in range(heads)],
+                           "rot": {"base": 1000000.0, "dims": dim}}}
+    listed = [dict(retention if i % 3 == 2 else parallel) for i in range(layers)]
+    return {"architecture": "Kasovik", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": listed}
+
+
+# Sizes that the layers of published decoders of 1.5 and 8 billion parameters have (width, heads, grouped keys, head
+# size 128, gated feed-forward), with windows of 1,024 and 2,048 tokens. Beside each the Qwen3 decoder of the same width,
+# heads, key heads, layers and feed-forward size.
+KASOVIK_SIZES = {
+    "base": (dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, ff=6144, layers=6),
+             dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=4, head_dim=128, intermediate_size=6144,
+                  num_hidden_layers=6, vocab_size=32768)),
+    "wide": (dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, ff=12288, layers=6),
+             dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                  num_hidden_layers=6, vocab_size=32768)),
+}
+
+
 def _find_number(data, key: str):
     """The first number stored under `key` anywhere in a nested JSON value (a dict under the key: its "value")."""
     if isinstance(data, dict):
@@ -531,15 +560,24 @@ def rulorax_run(args) -> dict:
     the same width, heads, layers and active feed-forward parameters: one 2,048-token prompt; decode steps at batch 1
     and 8 over 2,048-token contexts (through `Engine.step`, graphs on); and per-method microseconds of one eager step of
     each kind. Random weights; rooflines are worked out from these numbers in the design notes."""
+    return beside_qwen3(args, "rulorax", RULORAX_SIZES, rulorax_config, args.rulorax_sizes)
+
+
+def kasovik_run(args) -> dict:
+    """The same for Kasovik beside the Qwen3 decoder of the same width, heads, key heads, layers and feed-forward size."""
+    return beside_qwen3(args, "kasovik", KASOVIK_SIZES, kasovik_config, args.kasovik_sizes)
+
+
+def beside_qwen3(args, design: str, table: dict, make_config, chosen: str) -> dict:
     import gc
     import torch
     from holon_b200.engine import Engine, EngineConfig
     from holon_b200.weights import RandomSource
-    out = {"only": "rulorax", "sizes": {}}
+    out = {"only": design, "sizes": {}}
     steps = max(8, min(args.steps, 32))
-    for name in (args.rulorax_sizes.split(",") if args.rulorax_sizes else RULORAX_SIZES):
-        ours, theirs = RULORAX_SIZES[name]
-        models = {"rulorax": rulorax_config(**ours), "qwen3": dict(QWEN3_8B, **theirs)}
+    for name in (chosen.split(",") if chosen else table):
+        ours, theirs = table[name]
+        models = {design: make_config(**ours), "qwen3": dict(QWEN3_8B, **theirs)}
         result = {}
         for which, cfg in models.items():
             engine = Engine(EngineConfig(model=f"random weights, {which} {name}", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -674,6 +712,8 @@ def run_ours(args) -> dict:
         return shared_prompt_run(args)
     if args.only == "rulorax":
         return rulorax_run(args)
+    if args.only == "kasovik":
+        return kasovik_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -796,7 +836,7 @@ def main() -> int:
                          "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax", "kasovik"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
                          "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
                          "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
@@ -804,6 +844,7 @@ def main() -> int:
                          "rulorax: prefill and decode of the Rulorax design beside the Qwen3 decoder of equal size (--rulorax-sizes)")
     ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
     ap.add_argument("--rulorax-sizes", default="", help="with --only rulorax: which sizes (lite, small; default both)")
+    ap.add_argument("--kasovik-sizes", default="", help="with --only kasovik: which sizes (base, wide; default both)")
     ap.add_argument("--no-points", action="store_true", help="leave out the points at other batch sizes and contexts")
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-kernel table")
     args = ap.parse_args()

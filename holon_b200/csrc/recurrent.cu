@@ -23,9 +23,11 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ---------------------------------------------------------------- the scan
-// grid (rows, heads, column tiles); a thread owns the key channels d = i * P + p (i < DPT) of one value column, the P
-// threads of a column are neighbouring lanes. Tokens are staged in shared memory SC_TB at a time, so the loop over a
-// stage's tokens has no block-wide barrier: a token costs its multiply-adds and two sums over P lanes.
+// grid (rows, heads, column tiles); a thread owns DPT key channels of one value column, in groups of four that lie
+// side by side (group i4 of thread p: channels (i4 P + p) 4 .. + 3, so the P threads of a column, neighbouring lanes, read
+// a stage's k, q and decays as 16-byte pieces without bank conflicts). Tokens are staged in shared memory SC_TB at a
+// time, so the loop over a stage's tokens has no block-wide barrier: a token costs its multiply-adds and two sums over
+// P lanes.
 #define SC_TB 8
 
 template <int DPT>
@@ -34,7 +36,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                                       const float* __restrict__ beta, float* __restrict__ state,
                                       const int32_t* __restrict__ query_start, const int32_t* __restrict__ row_slot,
                                       int heads, int kv_heads, int dim, int vdim, int P, int VT, int tb) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * VT;
     const int hk = h / (heads / kv_heads);
     const int DP = P * DPT;
@@ -50,7 +52,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = i * P + p;
+        const int d = ((i >> 2) * P + p) * 4 + (i & 3);
         S[i] = col && d < dim ? S_g[(size_t)d * vdim + c] : 0.f;
     }
     const float fixed = head_decay ? head_decay[h] : 1.f;
@@ -72,13 +74,19 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         if ((int)threadIdx.x < m) sb[threadIdx.x] = beta ? beta[(size_t)(t0 + j0 + threadIdx.x) * heads + h] : 1.f;
         __syncthreads();
         for (int j = 0; j < m; ++j) {
-            const float* kj = sk + j * DP + p;
-            const float* qj = sq + j * DP + p;
+            const float4* kj = (const float4*)(sk + j * DP) + p;    // group i4 of this thread: kj[i4 * P]
+            const float4* qj = (const float4*)(sq + j * DP) + p;
             float u = cl < VT ? sv[j * VT + cl] : 0.f;               // (threads past the tile carry zeros: the sums below are warp-wide)
-            if (decay) {
-                const float* gj = sg + j * DP + p;
+            float4 k4[DPT / 4];
 #pragma unroll
-                for (int i = 0; i < DPT; ++i) S[i] *= gj[i * P];
+            for (int i = 0; i < DPT / 4; ++i) k4[i] = kj[i * P];
+            if (decay) {
+                const float4* gj = (const float4*)(sg + j * DP) + p;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 g = gj[i * P];
+                    S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) S[i] *= fixed;
@@ -86,18 +94,24 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
             if (beta) {
                 float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPT; i += 2) { a0 = fmaf(S[i], kj[i * P], a0); a1 = fmaf(S[i + 1], kj[(i + 1) * P], a1); }
+                for (int i = 0; i < DPT / 4; ++i) {
+                    a0 = fmaf(S[4 * i], k4[i].x, a0); a1 = fmaf(S[4 * i + 1], k4[i].y, a1);
+                    a0 = fmaf(S[4 * i + 2], k4[i].z, a0); a1 = fmaf(S[4 * i + 3], k4[i].w, a1);
+                }
                 float a = a0 + a1;
                 for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
                 u = sb[j] * (u - a);
             }
             float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < DPT; i += 2) {
-                S[i] = fmaf(kj[i * P], u, S[i]);
-                S[i + 1] = fmaf(kj[(i + 1) * P], u, S[i + 1]);
-                o0 = fmaf(S[i], qj[i * P], o0);
-                o1 = fmaf(S[i + 1], qj[(i + 1) * P], o1);
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 q4 = qj[i * P];
+                S[4 * i] = fmaf(k4[i].x, u, S[4 * i]);
+                S[4 * i + 1] = fmaf(k4[i].y, u, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(k4[i].z, u, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(k4[i].w, u, S[4 * i + 3]);
+                o0 = fmaf(S[4 * i], q4.x, o0); o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                o0 = fmaf(S[4 * i + 2], q4.z, o0); o1 = fmaf(S[4 * i + 3], q4.w, o1);
             }
             float o = o0 + o1;
             for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
@@ -106,7 +120,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
-        const int d = i * P + p;
+        const int d = ((i >> 2) * P + p) * 4 + (i & 3);
         if (col && d < dim) S_g[(size_t)d * vdim + c] = S[i];
     }
 }

@@ -317,22 +317,23 @@ int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, 
 
 // ---- mixers with a matrix state per head (csrc/recurrent.cu). Rows as for attention: row b brings tokens
 // query_start[b] .. query_start[b + 1] and lives in slot row_slot[b].
-// The scan. qk [tokens, 2, kv_heads, dim] (queries, then keys), v [tokens, heads, vdim], state [slots, heads, dim, vdim],
-// all 32-bit; head h reads key head h / (heads / kv_heads). Per token: S <- g S with g = decay[t, h, :] (per key channel)
+// The scan. qk [tokens, 2, kv_heads, dim] (queries, then keys), v [tokens, heads, vdim], state [slots, heads, vdim, dim]
+// (S column by column), all 32-bit; head h reads key head h / (heads / kv_heads). Per token: S <- g S with g = decay[t, h, :] (per key channel)
 // or head_decay[h] (give exactly one of the two); u = beta[t, h] (v - S^T k) (beta null: u = v); S <- S + k u^T;
-// out[t, h, :] = S^T q. The state is read at the start of a row and written back at its end.
+// out[t, h, :] = S^T q. The state is read at the start of a row and written back at its end. `most`: no row brings more
+// tokens than this (0: unknown); it bounds the stage of tokens a block keeps in shared memory.
 int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
                       const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
-                      int heads, int kv_heads, int dim, int vdim, hb_stream stream);
-// A delta-rule mixer's first product, rows [q | k | v | b | a1 | g1] of `dtype`, `ld` apart, becomes the scan's inputs:
-// q, k, v through a causal convolution over time (conv [channels, taps], carried inputs conv_state [slots, taps - 1,
-// channels]) and silu; q, k unit vectors per head (eps unit_eps), q times q_scale; beta = sigmoid(b);
-// decay = exp(-exp(rate_log[h]) softplus(a2 a1 + dt_bias)) [tokens, heads, dim]; gate = sigmoid(g2 g1) [tokens, heads vdim].
+                      int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream);
+// A delta-rule mixer's first product, rows [q | k | v | b] of `dtype`, `ld` apart, and the outputs of its two low-rank
+// projections, low2 [tokens, heads dim + heads vdim] in 32-bit, become the scan's inputs: q, k, v through a causal
+// convolution over time (conv [channels, taps], carried inputs conv_state [slots, taps - 1, channels]) and silu; q, k
+// unit vectors per head (eps unit_eps), q times q_scale; beta = sigmoid(b); decay = exp(-exp(rate_log[h])
+// softplus(low2[:, :heads dim] + dt_bias)) [tokens, heads, dim]; gate = sigmoid(low2[:, heads dim:]) [tokens, heads vdim].
 int hb_delta_prepare(float* qk, float* v, float* beta, float* decay, float* gate, const void* first, int dtype, int ld,
-                     const void* conv, int taps, const void* conv_state, const void* a2, const float* dt_bias,
-                     const float* rate_log, const void* g2, const int32_t* query_start, const int32_t* row_slot, int rows,
-                     int tokens, int heads, int kv_heads, int dim, int vdim, int ra, int rg, float q_scale,
-                     float unit_eps, hb_stream stream);
+                     const void* conv, int taps, const void* conv_state, const float* low2, const float* dt_bias,
+                     const float* rate_log, const int32_t* query_start, const int32_t* row_slot, int rows, int tokens,
+                     int heads, int kv_heads, int dim, int vdim, float q_scale, float unit_eps, hb_stream stream);
 // conv_state <- the last taps - 1 inputs of each row (what was carried, then the step's tokens). After hb_delta_prepare.
 int hb_conv_carry(void* conv_state, const void* first, int dtype, int ld, int channels, int taps,
                   const int32_t* query_start, const int32_t* row_slot, int rows, hb_stream stream);

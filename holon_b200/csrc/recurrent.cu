@@ -1,5 +1,6 @@
 // Mixers whose memory is a matrix per head instead of a cache of keys: S [key channel, value channel] in 32-bit per
-// request slot and head, updated token by token,
+// request slot and head (kept column by column: state [slots, heads, vdim, dim], so that the key channels a thread owns
+// lie side by side), updated token by token,
 //     S <- diag(g_t) S                      (g_t: a decay per key channel and token, or one fixed decay per head)
 //     u  = beta_t (v_t - S^T k_t)           (the delta rule; without beta: u = v_t)
 //     S <- S + k_t u^T,      o_t = S^T q_t  (the read-out sees the token's own write)
@@ -24,55 +25,101 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 
 // ---------------------------------------------------------------- the scan
 // grid (rows, heads, column tiles); a thread owns DPT key channels of one value column, in groups of four that lie
-// side by side (group i4 of thread p: channels (i4 P + p) 4 .. + 3, so the P threads of a column, neighbouring lanes, read
-// a stage's k, q and decays as 16-byte pieces without bank conflicts). Tokens are staged in shared memory SC_TB at a
-// time, so the loop over a stage's tokens has no block-wide barrier: a token costs its multiply-adds and two sums over
-// P lanes.
-#define SC_TB 8
+// side by side (group i4 of thread p: channels (i4 P + p) 4 .. + 3), and the P threads of a column are neighbouring lanes
+// that read a token's k, q and decays as 16-byte pieces without bank conflicts. With P = 32 a warp is a column, and the
+// many warps of an SM hide one another's waits: a token is a chain of multiply-adds and two sums over P lanes that no
+// width shortens. Tokens are staged in shared memory `tb` at a time by cp.async, a stage ahead of the one in work, so
+// the loop over a stage's tokens has no block-wide barrier and no wait for global memory.
+#define SC_TB 16
 
-template <int DPT>
+__device__ __forceinline__ void cp_async_f32(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int DPT, int P>
 __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qk, const float* __restrict__ v,
                                       const float* __restrict__ decay, const float* __restrict__ head_decay,
                                       const float* __restrict__ beta, float* __restrict__ state,
                                       const int32_t* __restrict__ query_start, const int32_t* __restrict__ row_slot,
-                                      int heads, int kv_heads, int dim, int vdim, int P, int VT, int tb) {
+                                      int heads, int kv_heads, int dim, int vdim, int VT, int tb) {
     extern __shared__ __align__(16) float sm[];
+    constexpr int DP = P * DPT;
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * VT;
     const int hk = h / (heads / kv_heads);
-    const int DP = P * DPT;
     const int p = threadIdx.x % P, cl = threadIdx.x / P, c = c0 + cl;
     const bool col = cl < VT && c < vdim;
     const int t0 = query_start[b], n = query_start[b + 1] - t0;
-    float* S_g = state + ((size_t)row_slot[b] * heads + h) * dim * vdim;
-    float* sq = sm;                          // [tb][DP]
-    float* sk = sq + tb * DP;                // [tb][DP]
-    float* sg = sk + tb * DP;                // [tb][DP]   (per-channel decays only)
-    float* sv = sg + (decay ? tb * DP : 0);  // [tb][VT]
-    float* sb = sv + tb * VT;                // [tb]
+    float* S_g = state + (((size_t)row_slot[b] * heads + h) * vdim + (col ? c : 0)) * dim;   // this thread's column
+    // a stage: q [tb][DP], k [tb][DP], decays [tb][DP] (per-channel decays only), v [tb][VT], beta [tb]; two of them
+    const int used = tb * ((decay ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
+    for (int e = threadIdx.x; e < 2 * per_stage; e += blockDim.x) {      // what no copy fills stays neutral: k = q = v = 0,
+        const int at = e % per_stage;                                    // decay = beta = 1
+        const bool one = (decay && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
+        sm[e] = one ? 1.f : 0.f;
+    }
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = ((i >> 2) * P + p) * 4 + (i & 3);
-        S[i] = col && d < dim ? S_g[(size_t)d * vdim + c] : 0.f;
+        S[i] = col && d < dim ? S_g[d] : 0.f;
     }
     const float fixed = head_decay ? head_decay[h] : 1.f;
-    for (int j0 = 0; j0 < n; j0 += tb) {
+    const bool vec = (dim & 3) == 0;
+    const int width = min(VT, vdim - c0);
+    __syncthreads();
+
+    auto fetch = [&](int j0, int which) {
+        float* sq = sm + which * per_stage;
+        float* sk = sq + tb * DP;
+        float* sg = sk + tb * DP;
+        float* sv = sg + (decay ? tb * DP : 0);
+        float* sb = sv + tb * VT;
         const int m = min(tb, n - j0);
-        __syncthreads();                                            // the stage before is read
-        for (int e = threadIdx.x; e < m * DP; e += blockDim.x) {
-            const int j = e / DP, d = e - j * DP;
-            const size_t t = (size_t)(t0 + j0 + j);
-            const bool in = d < dim;
-            sq[e] = in ? qk[((t * 2) * kv_heads + hk) * dim + d] : 0.f;
-            sk[e] = in ? qk[((t * 2 + 1) * kv_heads + hk) * dim + d] : 0.f;
-            if (decay) sg[e] = in ? decay[(t * heads + h) * dim + d] : 1.f;
+        if (vec) {
+            const int quads = dim >> 2;
+            for (int e = threadIdx.x; e < m * quads; e += blockDim.x) {
+                const int j = e / quads, d = (e - j * quads) * 4;
+                const size_t t = (size_t)(t0 + j0 + j);
+                cp_async_f32x4(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
+                cp_async_f32x4(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
+                if (decay) cp_async_f32x4(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+            }
+        } else {
+            for (int e = threadIdx.x; e < m * dim; e += blockDim.x) {
+                const int j = e / dim, d = e - j * dim;
+                const size_t t = (size_t)(t0 + j0 + j);
+                cp_async_f32(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
+                cp_async_f32(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
+                if (decay) cp_async_f32(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+            }
         }
-        for (int e = threadIdx.x; e < m * VT; e += blockDim.x) {
-            const int j = e / VT, x = e - j * VT;
-            sv[e] = c0 + x < vdim ? v[((size_t)(t0 + j0 + j) * heads + h) * vdim + c0 + x] : 0.f;
+        for (int e = threadIdx.x; e < m * width; e += blockDim.x) {
+            const int j = e / width, x = e - j * width;
+            cp_async_f32(sv + j * VT + x, v + ((size_t)(t0 + j0 + j) * heads + h) * vdim + c0 + x);
         }
-        if ((int)threadIdx.x < m) sb[threadIdx.x] = beta ? beta[(size_t)(t0 + j0 + threadIdx.x) * heads + h] : 1.f;
+        if (beta && (int)threadIdx.x < m) cp_async_f32(sb + threadIdx.x, beta + (size_t)(t0 + j0 + threadIdx.x) * heads + h);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    fetch(0, 0);
+    int which = 0;
+    for (int j0 = 0; j0 < n; j0 += tb, which ^= 1) {
+        const int m = min(tb, n - j0);
+        if (j0 + tb < n) {
+            fetch(j0 + tb, which ^ 1);                                  // (that buffer was read a stage ago: barrier below)
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
+        const float* sq = sm + which * per_stage;
+        const float* sk = sq + tb * DP;
+        const float* sg = sk + tb * DP;
+        const float* sv = sg + (decay ? tb * DP : 0);
+        const float* sb = sv + tb * VT;
         for (int j = 0; j < m; ++j) {
             const float4* kj = (const float4*)(sk + j * DP) + p;    // group i4 of this thread: kj[i4 * P]
             const float4* qj = (const float4*)(sq + j * DP) + p;
@@ -99,6 +146,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                     a0 = fmaf(S[4 * i + 2], k4[i].z, a0); a1 = fmaf(S[4 * i + 3], k4[i].w, a1);
                 }
                 float a = a0 + a1;
+#pragma unroll
                 for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
                 u = sb[j] * (u - a);
             }
@@ -114,132 +162,143 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 o0 = fmaf(S[4 * i + 2], q4.z, o0); o1 = fmaf(S[4 * i + 3], q4.w, o1);
             }
             float o = o0 + o1;
+#pragma unroll
             for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (p == 0 && col) out[((size_t)(t0 + j0 + j) * heads + h) * vdim + c] = o;
         }
+        __syncthreads();                                            // this stage is read: the next fetch may fill it
     }
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = ((i >> 2) * P + p) * 4 + (i & 3);
-        if (col && d < dim) S_g[(size_t)d * vdim + c] = S[i];
+        if (col && d < dim) S_g[d] = S[i];
     }
 }
 
-extern "C" int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                                 const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
-                                 int rows, int heads, int kv_heads, int dim, int vdim, hb_stream stream) {
-    if (rows == 0) return 0;
-    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("recurrent_scan: %d heads are no multiple of %d key heads", heads, kv_heads);
-    if (dim < 1 || dim > 1024 || vdim < 1) HB_REFUSE("recurrent_scan: key size %d (1 to 1024), value size %d", dim, vdim);
-    if ((decay != nullptr) == (head_decay != nullptr)) HB_REFUSE("recurrent_scan: give decays per channel and token, or one per head");
-    if (rows > 65535 * 32 || heads > 65535) HB_REFUSE("recurrent_scan: %d rows, %d heads", rows, heads);
-    const int dpt = dim <= 64 ? 8 : dim <= 128 ? 16 : 32;
-    int P = 1;
-    while (P * dpt < dim) P <<= 1;
+template <int DPT, int P>
+static int launch_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
+                       const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
+                       int heads, int kv_heads, int dim, int vdim, int most, cudaStream_t s) {
     const int unit = 32 / P > 1 ? 32 / P : 1;                         // columns a warp holds
     int VT = vdim < 256 / P ? vdim : 256 / P;
     if (VT < 1) VT = 1;
     const int threads = ((VT + unit - 1) / unit) * unit * P;
     const int tiles = (vdim + VT - 1) / VT;
-    const int DP = P * dpt;
-    const int per_token = (decay ? 3 : 2) * DP + VT + 1;
-    int tb = 48 * 1024 / 4 / per_token;
+    const int per_token = (decay ? 3 : 2) * P * DPT + VT + 1;
+    int tb = 96 * 1024 / 8 / per_token;                               // two stages in at most 96 KB
     if (tb > SC_TB) tb = SC_TB;
     if (tb < 1) HB_REFUSE("recurrent_scan: key size %d needs more shared memory than a block has", dim);
     if (tb > threads) tb = threads;
-    const size_t smem = (size_t)tb * per_token * sizeof(float);
-    dim3 grid(rows, heads, tiles);
-    cudaStream_t s = (cudaStream_t)stream;
-#define HB_SCAN(D) recurrent_scan_kernel<D><<<grid, threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, \
-    query_start, row_slot, heads, kv_heads, dim, vdim, P, VT, tb)
-    if (dpt == 8) HB_SCAN(8); else if (dpt == 16) HB_SCAN(16); else HB_SCAN(32);
-#undef HB_SCAN
+    if (most > 0 && tb > most) tb = most;                             // (no row brings more tokens than that)
+    const size_t smem = (size_t)2 * ((tb * per_token + 3) & ~3) * sizeof(float);
+    auto kernel = recurrent_scan_kernel<DPT, P>;
+    if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<dim3(rows, heads, tiles), threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot,
+                                                          heads, kv_heads, dim, vdim, VT, tb);
     HB_LAUNCH_CHECK("recurrent_scan");
     return 0;
 }
 
+extern "C" int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
+                                 const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
+                                 int rows, int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("recurrent_scan: %d heads are no multiple of %d key heads", heads, kv_heads);
+    if (dim < 1 || dim > 1024 || vdim < 1) HB_REFUSE("recurrent_scan: key size %d (1 to 1024), value size %d", dim, vdim);
+    if ((decay != nullptr) == (head_decay != nullptr)) HB_REFUSE("recurrent_scan: give decays per channel and token, or one per head");
+    if (rows > 65535 * 32 || heads > 65535 || (vdim + 7) / 8 > 65535) HB_REFUSE("recurrent_scan: %d rows, %d heads, value size %d", rows, heads, vdim);
+    if ((((uintptr_t)qk | (uintptr_t)decay) & 15) != 0) HB_REFUSE("recurrent_scan: qk and decay must lie on 16-byte boundaries");
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_SCAN(D, PP) return launch_scan<D, PP>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot, rows, heads, \
+                                                 kv_heads, dim, vdim, most, s)
+    // Four channels a thread up to a key size of 64, then more channels a thread. (Key size 128, 2,048 tokens of 16 heads,
+    // microseconds a token with the delta rule: 16 lanes of 8 channels 0.37, 32 lanes of 4 0.40, 8 lanes of 16 0.40, 4 lanes of
+    // 32 0.51: a token is one chain of dependent steps whatever the lanes, and the warps of an SM fill one another's gaps.)
+    if (dim <= 4) HB_SCAN(4, 1);
+    if (dim <= 8) HB_SCAN(4, 2);
+    if (dim <= 16) HB_SCAN(4, 4);
+    if (dim <= 32) HB_SCAN(4, 8);
+    if (dim <= 64) HB_SCAN(4, 16);
+    if (dim <= 128) HB_SCAN(8, 16);
+    if (dim <= 256) HB_SCAN(8, 32);
+    if (dim <= 512) HB_SCAN(16, 32);
+    HB_SCAN(32, 32);
+#undef HB_SCAN
+}
+
 // ---------------------------------------------------------------- what the delta-rule mixer's first product becomes
-// A token's row of `first` holds [q (kv_heads dim) | k (kv_heads dim) | v (heads vdim) | b (heads) | a1 (ra) | g1 (rg)].
+// A token's row of `first` holds [q (kv_heads dim) | k (kv_heads dim) | v (heads vdim) | b (heads)], its row of `low2`
+// (32-bit) the outputs of the two low-rank projections [a (heads dim) | g (heads vdim)].
 // q, k, v pass a causal convolution over time (weights conv [channels, taps], the last tap the token's own; inputs
 // before the step's first token of the row come from conv_state [slots, taps - 1, channels], oldest first) and silu;
 // q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale. beta = sigmoid(b).
-// decay[h, d] = exp(-exp(rate_log[h]) softplus(a2[h dim + d] . a1 + dt_bias[h dim + d])), gate = sigmoid(g2 . g1).
-// One block per token.
+// decay[h, d] = exp(-exp(rate_log[h]) softplus(a[h dim + d] + dt_bias[h dim + d])), gate = sigmoid(g).
+// grid (tokens, segments): the first segments take the q and k heads, a warp a head (the convolution twice: once for the
+// sum of squares, once for the values); the others an element a thread of v, beta, the decays and the gate. No thread
+// waits for another, so a step of a few tokens still spreads over many blocks.
 template <typename T>
 __global__ void delta_prepare_kernel(float* __restrict__ qk, float* __restrict__ v, float* __restrict__ beta,
                                      float* __restrict__ decay, float* __restrict__ gate, const T* __restrict__ first,
                                      int ld, const T* __restrict__ conv, int taps, const T* __restrict__ conv_state,
-                                     const T* __restrict__ a2, const float* __restrict__ dt_bias, const float* __restrict__ rate_log,
-                                     const T* __restrict__ g2, const int32_t* __restrict__ query_start,
+                                     const float* __restrict__ low2, const float* __restrict__ dt_bias,
+                                     const float* __restrict__ rate_log, const int32_t* __restrict__ query_start,
                                      const int32_t* __restrict__ row_slot, int rows, int heads, int kv_heads, int dim,
-                                     int vdim, int ra, int rg, float q_scale, float unit_eps) {
-    extern __shared__ float sm[];
-    const int t = blockIdx.x;
+                                     int vdim, float q_scale, float unit_eps) {
+    const int t = blockIdx.x, seg = blockIdx.y;
     const int b = row_of_token(query_start, rows, t);
     const int t0 = query_start[b];
     const int nq = kv_heads * dim, nv = heads * vdim, C = 2 * nq + nv;
-    float* y = sm;                 // [C] after convolution and silu
-    float* low = y + C;            // [ra + rg] the low-rank inputs
     const T* st = conv_state ? conv_state + (size_t)row_slot[b] * (taps - 1) * C : nullptr;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    auto channel = [&](int c) -> float {                               // convolution over time and silu of channel c
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
-            const int back = taps - 1 - j;                           // how many tokens before t
-            float x;
-            if (t - back >= t0) x = to_f32(first[(size_t)(t - back) * ld + c]);
-            else x = to_f32(st[(size_t)(taps - 1 + (t - back - t0)) * C + c]);
+            const int at = t - (taps - 1 - j);                           // the token this tap weighs
+            const float x = at >= t0 ? to_f32(first[(size_t)at * ld + c]) : to_f32(st[(size_t)(taps - 1 + (at - t0)) * C + c]);
             acc = fmaf(to_f32(conv[(size_t)c * taps + j]), x, acc);
         }
-        y[c] = silu_f(acc);
-    }
-    const T* row = first + (size_t)t * ld;
-    for (int i = threadIdx.x; i < ra + rg; i += blockDim.x) low[i] = to_f32(row[C + heads + i]);
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int g = warp; g < 2 * kv_heads; g += warps) {               // unit vectors: q heads, then k heads
-        const float* x = y + (size_t)g * dim;
+        return silu_f(acc);
+    };
+    const int head_segments = (2 * kv_heads + 7) / 8;
+    if (seg < head_segments) {                                          // unit vectors: q heads, then k heads
+        const int g = seg * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+        if (g >= 2 * kv_heads) return;
         float ss = 0.f;
-        for (int d = lane; d < dim; d += 32) ss += x[d] * x[d];
-        ss = warp_sum(ss);
-        const float f = rsqrtf(ss + unit_eps) * (g < kv_heads ? q_scale : 1.f);
-        for (int d = lane; d < dim; d += 32) qk[((size_t)t * 2 * kv_heads + g) * dim + d] = x[d] * f;
+        for (int d = lane; d < dim; d += 32) { const float x = channel(g * dim + d); ss = fmaf(x, x, ss); }
+        const float f = rsqrtf(warp_sum(ss) + unit_eps) * (g < kv_heads ? q_scale : 1.f);
+        for (int d = lane; d < dim; d += 32) qk[((size_t)t * 2 * kv_heads + g) * dim + d] = channel(g * dim + d) * f;
+        return;
     }
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) v[(size_t)t * nv + i] = y[2 * nq + i];
-    for (int i = threadIdx.x; i < heads; i += blockDim.x) beta[(size_t)t * heads + i] = sigmoid_f(to_f32(row[C + i]));
-    for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
-        float a = dt_bias[i];
-        const T* w = a2 + (size_t)i * ra;
-        for (int r = 0; r < ra; ++r) a = fmaf(to_f32(w[r]), low[r], a);
-        decay[(size_t)t * heads * dim + i] = expf(-expf(rate_log[i / dim]) * softplus_f(a));
+    int e = (seg - head_segments) * blockDim.x + threadIdx.x;
+    if (e < nv) { v[(size_t)t * nv + e] = channel(2 * nq + e); return; }
+    e -= nv;
+    if (e < heads) { beta[(size_t)t * heads + e] = sigmoid_f(to_f32(first[(size_t)t * ld + C + e])); return; }
+    e -= heads;
+    const float* z = low2 + (size_t)t * (heads * dim + nv);
+    if (e < heads * dim) {
+        decay[(size_t)t * heads * dim + e] = expf(-expf(rate_log[e / dim]) * softplus_f(z[e] + dt_bias[e]));
+        return;
     }
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-        float a = 0.f;
-        const T* w = g2 + (size_t)i * rg;
-        for (int r = 0; r < rg; ++r) a = fmaf(to_f32(w[r]), low[ra + r], a);
-        gate[(size_t)t * nv + i] = sigmoid_f(a);
-    }
+    e -= heads * dim;
+    if (e < nv) gate[(size_t)t * nv + e] = sigmoid_f(z[heads * dim + e]);
 }
 
 extern "C" int hb_delta_prepare(float* qk, float* v, float* beta, float* decay, float* gate, const void* first, int dtype,
-                                int ld, const void* conv, int taps, const void* conv_state, const void* a2,
-                                const float* dt_bias, const float* rate_log, const void* g2, const int32_t* query_start,
+                                int ld, const void* conv, int taps, const void* conv_state, const float* low2,
+                                const float* dt_bias, const float* rate_log, const int32_t* query_start,
                                 const int32_t* row_slot, int rows, int tokens, int heads, int kv_heads, int dim, int vdim,
-                                int ra, int rg, float q_scale, float unit_eps, hb_stream stream) {
+                                float q_scale, float unit_eps, hb_stream stream) {
     if (tokens == 0) return 0;
     if (taps < 1 || (taps > 1 && !conv_state)) HB_REFUSE("delta_prepare: %d taps need the carried inputs", taps);
-    const int C = 2 * kv_heads * dim + heads * vdim;
-    const size_t smem = (size_t)(C + ra + rg) * sizeof(float);
-    if (smem > 200 * 1024) HB_REFUSE("delta_prepare: %d channels are more than a block's shared memory holds", C);
+    const long elements = 2L * heads * vdim + heads + (long)heads * dim;
+    const long segments = (2 * kv_heads + 7) / 8 + (elements + 255) / 256;
+    if (segments > 65535) HB_REFUSE("delta_prepare: %ld segments a token are above 65535", segments);
+    dim3 grid(tokens, (unsigned)segments);
     cudaStream_t s = (cudaStream_t)stream;
-#define HB_ARGS(T) (const T*)first, ld, (const T*)conv, taps, (const T*)conv_state, (const T*)a2, dt_bias, \
-    rate_log, (const T*)g2, query_start, row_slot, rows, heads, kv_heads, dim, vdim, ra, rg, q_scale, unit_eps
-    if (dtype == HB_F32) {
-        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        delta_prepare_kernel<float><<<tokens, 256, smem, s>>>(qk, v, beta, decay, gate, HB_ARGS(float));
-    } else if (dtype == HB_BF16) {
-        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        delta_prepare_kernel<bf16><<<tokens, 256, smem, s>>>(qk, v, beta, decay, gate, HB_ARGS(bf16));
-    } else HB_REFUSE("delta_prepare: dtype %d", dtype);
+#define HB_ARGS(T) (const T*)first, ld, (const T*)conv, taps, (const T*)conv_state, low2, dt_bias, rate_log, \
+    query_start, row_slot, rows, heads, kv_heads, dim, vdim, q_scale, unit_eps
+    if (dtype == HB_F32) delta_prepare_kernel<float><<<grid, 256, 0, s>>>(qk, v, beta, decay, gate, HB_ARGS(float));
+    else if (dtype == HB_BF16) delta_prepare_kernel<bf16><<<grid, 256, 0, s>>>(qk, v, beta, decay, gate, HB_ARGS(bf16));
+    else HB_REFUSE("delta_prepare: dtype %d", dtype);
 #undef HB_ARGS
     HB_LAUNCH_CHECK("delta_prepare");
     return 0;
@@ -276,7 +335,7 @@ extern "C" int hb_conv_carry(void* conv_state, const void* first, int dtype, int
 // ---------------------------------------------------------------- what the retention mixer's first product becomes
 // A token's row of `first` holds [q (heads dim) | k (heads dim) | v (heads vdim) | ...]. q and k turn by the token's
 // position (the first rot_dims channels of a head, half-split pairs, table [positions, rot_dims]: cosines then sines),
-// k is then scaled. One block per token.
+// k is then scaled. grid (tokens, segments of 256 elements).
 template <typename T>
 __global__ void retention_prepare_kernel(float* __restrict__ qk, float* __restrict__ v, const T* __restrict__ first, int ld,
                                          const int32_t* __restrict__ positions, const float* __restrict__ table,
@@ -286,14 +345,17 @@ __global__ void retention_prepare_kernel(float* __restrict__ qk, float* __restri
     const int pos = min(max(positions[t], 0), max_positions > 0 ? max_positions - 1 : 0);
     const float* cs = table ? table + (size_t)pos * rot_dims : nullptr;
     const int half = rot_dims >> 1, nq = heads * dim;
-    for (int e = threadIdx.x; e < 2 * nq; e += blockDim.x) {
+    int e = blockIdx.y * blockDim.x + threadIdx.x;                       // an element a thread: q and k, then v
+    if (e < 2 * nq) {
         const int d = e % dim;
         float x = to_f32(row[e]);
         if (d < half) x = x * cs[d] - to_f32(row[e + half]) * cs[half + d];
         else if (d < rot_dims) x = x * cs[d - half] + to_f32(row[e - half]) * cs[d];
         qk[t * 2 * nq + e] = e >= nq ? x * k_scale : x;
+        return;
     }
-    for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) v[t * heads * vdim + e] = to_f32(row[2 * nq + e]);
+    e -= 2 * nq;
+    if (e < heads * vdim) v[t * heads * vdim + e] = to_f32(row[2 * nq + e]);
 }
 
 extern "C" int hb_retention_prepare(float* qk, float* v, const void* first, int dtype, int ld, const int32_t* positions,
@@ -303,8 +365,11 @@ extern "C" int hb_retention_prepare(float* qk, float* v, const void* first, int 
     if (rot_dims % 2 || rot_dims < 0 || rot_dims > dim) HB_REFUSE("retention_prepare: %d rotated channels of %d", rot_dims, dim);
     if (rot_dims && !table) HB_REFUSE("retention_prepare: a rotation needs its table");
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == HB_F32) retention_prepare_kernel<float><<<tokens, 256, 0, s>>>(qk, v, (const float*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
-    else if (dtype == HB_BF16) retention_prepare_kernel<bf16><<<tokens, 256, 0, s>>>(qk, v, (const bf16*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
+    const long segments = (2L * heads * dim + (long)heads * vdim + 255) / 256;
+    if (segments > 65535) HB_REFUSE("retention_prepare: %ld segments a token are above 65535", segments);
+    const dim3 tokens_by_segments(tokens, (unsigned)segments);
+    if (dtype == HB_F32) retention_prepare_kernel<float><<<tokens_by_segments, 256, 0, s>>>(qk, v, (const float*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
+    else if (dtype == HB_BF16) retention_prepare_kernel<bf16><<<tokens_by_segments, 256, 0, s>>>(qk, v, (const bf16*)first, ld, positions, table, rot_dims, max_positions, heads, dim, vdim, k_scale);
     else HB_REFUSE("retention_prepare: dtype %d", dtype);
     HB_LAUNCH_CHECK("retention_prepare");
     return 0;

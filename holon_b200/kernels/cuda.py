@@ -981,33 +981,35 @@ class CudaKernels:
         self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state)
         t, heads, vdim = v.shape
         kv_heads, dim = qk.shape[2], qk.shape[3]
-        if qk.shape != (t, 2, kv_heads, dim) or out.shape != v.shape or state.shape[1:] != (heads, dim, vdim) \
+        if qk.shape != (t, 2, kv_heads, dim) or out.shape != v.shape or state.shape[1:] != (heads, vdim, dim) \
                 or (decay is not None and decay.shape != (t, heads, dim)) or (beta is not None and beta.shape != (t, heads)) \
                 or (head_decay is not None and head_decay.shape != (heads,)):
             raise KernelError("recurrent_scan: qk [tokens, 2, kv_heads, dim], v and out [tokens, heads, vdim], state "
-                              "[slots, heads, dim, vdim], decay [tokens, heads, dim] or head_decay [heads], beta [tokens, heads]")
+                              "[slots, heads, vdim, dim], decay [tokens, heads, dim] or head_decay [heads], beta [tokens, heads]")
         self._call("hb_recurrent_scan", self._p(out), self._p(qk), self._p(v), self._p(decay), self._p(head_decay),
                    self._p(beta), self._p(state), self._i32(rows.query_start, "query_start"),
-                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, heads, kv_heads, dim, vdim)
+                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, heads, kv_heads, dim, vdim,
+                   int(getattr(rows, "max_q", 0) or 0))
 
-    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows, q_scale,
+    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, low2, dt_bias, rate_log, rows, q_scale,
                       unit_eps) -> None:
-        """From a delta-rule mixer's first product to the scan's inputs (csrc/api.h: hb_delta_prepare)."""
-        self._check(qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows.query_start, rows.row_slot)
-        self._f32("delta_prepare", qk, v, beta, decay, gate, dt_bias, rate_log)
+        """From a delta-rule mixer's first product and its low-rank projections' outputs to the scan's inputs
+        (csrc/api.h: hb_delta_prepare)."""
+        self._check(qk, v, beta, decay, gate, first, conv, conv_state, low2, dt_bias, rate_log, rows.query_start, rows.row_slot)
+        self._f32("delta_prepare", qk, v, beta, decay, gate, low2, dt_bias, rate_log)
         t, heads, vdim = v.shape
         kv_heads, dim = qk.shape[2], qk.shape[3]
-        ra, rg, taps = a2.shape[1], g2.shape[1], conv.shape[1]
+        taps = conv.shape[1]
         channels = 2 * kv_heads * dim + heads * vdim
-        if first.shape != (t, channels + heads + ra + rg) or conv.shape[0] != channels or a2.shape[0] != heads * dim \
-                or g2.shape[0] != heads * vdim or any(x.dtype != first.dtype for x in (conv, a2, g2)) \
+        if first.shape != (t, channels + heads) or conv.shape[0] != channels or conv.dtype != first.dtype \
+                or low2.shape != (t, heads * dim + heads * vdim) \
                 or (taps > 1 and (conv_state is None or conv_state.shape[1:] != (taps - 1, channels) or conv_state.dtype != first.dtype)):
-            raise KernelError("delta_prepare: first [tokens, q | k | v | b | a1 | g1], conv [channels, taps], conv_state "
-                              "[slots, taps - 1, channels], a2 [heads dim, ra], g2 [heads vdim, rg], of one dtype")
+            raise KernelError("delta_prepare: first [tokens, q | k | v | b], conv [channels, taps], conv_state [slots, "
+                              "taps - 1, channels] of one dtype, low2 float32 [tokens, heads dim + heads vdim]")
         self._call("hb_delta_prepare", self._p(qk), self._p(v), self._p(beta), self._p(decay), self._p(gate),
-                   self._p(first), _code(first), first.shape[1], self._p(conv), taps, self._p(conv_state), self._p(a2),
-                   self._p(dt_bias), self._p(rate_log), self._p(g2), self._i32(rows.query_start, "query_start"),
-                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, t, heads, kv_heads, dim, vdim, ra, rg,
+                   self._p(first), _code(first), first.shape[1], self._p(conv), taps, self._p(conv_state), self._p(low2),
+                   self._p(dt_bias), self._p(rate_log), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, t, heads, kv_heads, dim, vdim,
                    ctypes.c_float(q_scale), ctypes.c_float(unit_eps))
 
     def conv_carry(self, conv_state, first, channels, taps, rows) -> None:

@@ -1,7 +1,7 @@
 """Mixers whose memory is a matrix per head and request instead of a cache of keys.
 
-Both keep S [key channel, value channel] in 32-bit per request slot and head (`SlotState`), zero at admission, and
-update it token by token with the kernel table's `recurrent_scan`:
+Both keep S [key channel, value channel] in 32-bit per request slot and head (`SlotState`, stored column by column:
+[heads, vdim, dim]), zero at admission, and update it token by token with the kernel table's `recurrent_scan`:
 
     S ← diag(g_t) S;   u = β_t (v_t − Sᵀ k_t)  (or u = v_t);   S ← S + k_t uᵀ;   o_t = Sᵀ q_t.
 
@@ -33,7 +33,7 @@ class _MatrixState(Part):
         return None
 
     def _strip(self, prefix: str, name: str) -> str:
-        for child in ("first.", "out."):
+        for child in ("first.", "low.", "out."):
             if name.startswith(prefix + child):
                 return prefix + name[len(prefix + child):]
         return name
@@ -63,7 +63,7 @@ class Retention(_MatrixState):
             self._decay = torch.tensor(self.decay, dtype=torch.float32, device=self.first.weight.tensor.device)
 
     def slot_states(self):
-        return (SlotState("state", (self.heads, self.dim, self.vdim)),)
+        return (SlotState("state", (self.heads, self.vdim, self.dim)),)
 
     def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
         t, k, ctx, heads, dim, vdim = x.shape[0], self.ctx.kernels, self.ctx, self.heads, self.dim, self.vdim
@@ -95,8 +95,9 @@ class GatedDelta(_MatrixState):
         self.taps, self.eps = int(taps), float(eps)
         nq, nv = kv_heads * dim, heads * vdim
         self.channels = 2 * nq + nv
-        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {
-            "q": nq, "k": nq, "v": nv, "b": heads, "a1": decay_rank, "g1": gate_rank}))
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {"q": nq, "k": nq, "v": nv, "b": heads}))
+        self.low = self.add_child("low", Linear(ctx, "weight", hidden, {"a1": decay_rank, "g1": gate_rank}))
+        self.second = None                 # [heads dim + heads vdim, ranks]: a2 and g2 as one block-diagonal weight (finalize)
         self.conv = self.add_param("conv", (self.channels, taps), "matrix",
                                    {"q.conv": (0, nq), "k.conv": (nq, 2 * nq), "v.conv": (2 * nq, self.channels)})
         self.a2 = self.add_param("a2", (heads * dim, decay_rank), "matrix")
@@ -106,8 +107,16 @@ class GatedDelta(_MatrixState):
         self.gain = self.add_param("norm", (vdim,), "coef")
         self.out = self.add_child("out", Linear(ctx, "weight", nv, {"o": hidden}))
 
+    def finalize(self) -> None:
+        super().finalize()
+        a2, g2 = self.a2.tensor, self.g2.tensor
+        if a2 is not None and g2 is not None:                 # one product for both low-rank second projections
+            self.second = torch.zeros(a2.shape[0] + g2.shape[0], a2.shape[1] + g2.shape[1], dtype=a2.dtype, device=a2.device)
+            self.second[:a2.shape[0], :a2.shape[1]].copy_(a2)
+            self.second[a2.shape[0]:, a2.shape[1]:].copy_(g2)
+
     def slot_states(self):
-        states = [SlotState("state", (self.heads, self.dim, self.vdim))]
+        states = [SlotState("state", (self.heads, self.vdim, self.dim))]
         if self.taps > 1:
             dtype = str(self.ctx.dtype).replace("torch.", "")
             states.append(SlotState("conv", (self.taps - 1, self.channels), dtype))
@@ -117,13 +126,15 @@ class GatedDelta(_MatrixState):
         t, k, ctx = x.shape[0], self.ctx.kernels, self.ctx
         heads, kvh, dim, vdim = self.heads, self.kv_heads, self.dim, self.vdim
         f32 = torch.float32
-        first = self.first.forward(x)                                    # [t, q | k | v | b | a1 | g1]
+        first = self.first.forward(x)                                    # [t, q | k | v | b]
+        low2 = ctx.empty(t, self.second.shape[0], dtype=f32)             # [t, a | g]: W_a2 (W_a1 x) and W_g2 (W_g1 x)
+        k.linear(low2, self.low.forward(x), self.second)
         qk, v = ctx.empty(t, 2, kvh, dim, dtype=f32), ctx.empty(t, heads, vdim, dtype=f32)
         beta, decay = ctx.empty(t, heads, dtype=f32), ctx.empty(t, heads, dim, dtype=f32)
         gate = ctx.empty(t, heads * vdim, dtype=f32)
         carried = cache.slots.get("conv")
-        k.delta_prepare(qk, v, beta, decay, gate, first, self.conv.tensor, carried, self.a2.tensor, self.dt_bias.tensor,
-                        self.rate_log.tensor, self.g2.tensor, step.rows, dim ** -0.5, self.UNIT_EPS)
+        k.delta_prepare(qk, v, beta, decay, gate, first, self.conv.tensor, carried, low2, self.dt_bias.tensor,
+                        self.rate_log.tensor, step.rows, dim ** -0.5, self.UNIT_EPS)
         k.conv_carry(carried, first, self.channels, self.taps, step.rows)
         o = ctx.empty(t, heads, vdim, dtype=f32)
         k.recurrent_scan(o, qk, v, decay, None, beta, cache.slots["state"], step.rows)

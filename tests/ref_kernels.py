@@ -136,20 +136,20 @@ class RefKernels:
         qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
         for b in range(rows.n_rows):
             for h in range(heads):
-                s = state[slots[b], h].clone()
+                s = state[slots[b], h].T.clone()               # (kept column by column: [vdim, dim])
                 for i in range(qs[b], qs[b + 1]):
                     q, k = qk[i, 0, h // group], qk[i, 1, h // group]
                     s = s * (decay[i, h][:, None] if decay is not None else head_decay[h])
                     u = v[i, h] if beta is None else beta[i, h] * (v[i, h] - s.T @ k)
                     s = s + torch.outer(k, u)
                     out[i, h] = s.T @ q
-                state[slots[b], h] = s
+                state[slots[b], h] = s.T
 
-    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, a2, dt_bias, rate_log, g2, rows, q_scale,
+    def delta_prepare(self, qk, v, beta, decay, gate, first, conv, conv_state, low2, dt_bias, rate_log, rows, q_scale,
                       unit_eps):
         t, heads, vdim = v.shape
         kv_heads, dim = qk.shape[2], qk.shape[3]
-        taps, ra, rg = conv.shape[1], a2.shape[1], g2.shape[1]
+        taps = conv.shape[1]
         nq, nv = kv_heads * dim, heads * vdim
         c = 2 * nq + nv
         x = first.float()
@@ -166,9 +166,9 @@ class RefKernels:
         qk[:, 1] = unit(y[:, nq:2 * nq].view(t, kv_heads, dim))
         v.copy_(y[:, 2 * nq:].view(t, heads, vdim))
         beta.copy_(torch.sigmoid(x[:, c:c + heads]))
-        a = x[:, c + heads:c + heads + ra] @ a2.float().T + dt_bias
+        a = low2[:, :heads * dim] + dt_bias
         decay.copy_(torch.exp(-torch.exp(rate_log)[None, :, None] * torch.nn.functional.softplus(a).view(t, heads, dim)))
-        gate.copy_(torch.sigmoid(x[:, c + heads + ra:] @ g2.float().T).view(gate.shape))
+        gate.copy_(torch.sigmoid(low2[:, heads * dim:]).view(gate.shape))
 
     def conv_carry(self, conv_state, first, channels, taps, rows):
         if taps <= 1:

@@ -71,7 +71,7 @@ def test_recurrent_scan(K, heads, kv_heads, dim, vdim, mode):
     decay = torch.sigmoid(rand(t, heads, dim, seed=3) + 2.0) if mode == "delta" else None
     fixed = torch.tensor([0.9, 0.99, 0.5, 0.97][:heads]) if mode == "fixed" else None
     beta = torch.sigmoid(rand(t, heads, seed=4)) if mode == "delta" else None
-    state = rand(7, heads, dim, vdim, seed=5) * 0.3
+    state = rand(7, heads, vdim, dim, seed=5) * 0.3
     sg, sw = state.clone().to(DEV), state.clone()
     for _ in range(2):
         out, want = torch.full((t, heads, vdim), float("nan"), device=DEV), torch.zeros(t, heads, vdim)
@@ -96,35 +96,34 @@ def test_the_scan_keeps_a_far_write(K):
     v = rand(t, 1, vdim, seed=2)
     for decay, kept in ((0.999, 0.999 ** 600), (0.9, 0.0)):
         out = torch.empty(t, 1, vdim, device=DEV)
-        state = torch.zeros(1, 1, dim, vdim, device=DEV)
+        state = torch.zeros(1, 1, vdim, dim, device=DEV)
         K.recurrent_scan(out, qk.to(DEV), v.to(DEV), None, torch.tensor([decay], device=DEV), None, state, rows_of([t], [0]))
         assert torch.allclose(out[603, 0].cpu(), kept * v[3, 0], atol=1e-5)
 
 
 # ---------------------------------------------------------------- from the first product to the scan's inputs
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,ra,rg", [(4, 2, 16, 32, 4, 8, 12), (6, 2, 12, 20, 2, 5, 7), (2, 2, 96, 80, 1, 16, 16),
-                                                                (3, 3, 8, 8, 7, 3, 2)])
-def test_delta_prepare_and_the_carried_inputs(K, dtype, heads, kv_heads, dim, vdim, taps, ra, rg):
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps", [(4, 2, 16, 32, 4), (6, 2, 12, 20, 2), (2, 2, 96, 80, 1), (3, 3, 8, 8, 7)])
+def test_delta_prepare_and_the_carried_inputs(K, dtype, heads, kv_heads, dim, vdim, taps):
     """Rows of 1, 2, 5 and 9 tokens: shorter than, as long as and longer than the convolution's reach, so the carried
     inputs are read, shifted and replaced; three steps in a row on the same slots."""
     counts, slots = [1, 2, 5, 9], [2, 0, 3, 1]
     t = sum(counts)
     nq, nv = kv_heads * dim, heads * vdim
     c = 2 * nq + nv
-    conv, a2, g2 = rand(c, taps, dtype=dtype, seed=1, scale=0.6), rand(heads * dim, ra, dtype=dtype, seed=2, scale=0.5), rand(nv, rg, dtype=dtype, seed=3, scale=0.5)
+    conv = rand(c, taps, dtype=dtype, seed=1, scale=0.6)
     dt_bias, rate_log = rand(heads * dim, seed=4), rand(heads, seed=5) - 1.0
     carried = rand(5, max(taps - 1, 0), c, dtype=dtype, seed=6) if taps > 1 else None
     cg, cw = (carried.clone().to(DEV), carried.clone()) if taps > 1 else (None, None)
     for step in range(3):
-        first = rand(t, c + heads + ra + rg, dtype=dtype, seed=10 + step)
+        first, low2 = rand(t, c + heads, dtype=dtype, seed=10 + step), rand(t, heads * dim + nv, seed=20 + step, scale=2.0)
         shapes = [(t, 2, kv_heads, dim), (t, heads, vdim), (t, heads), (t, heads, dim), (t, nv)]
         got = [torch.full(s, float("nan"), device=DEV) for s in shapes]
         want = [torch.zeros(s) for s in shapes]
-        K.delta_prepare(*got, first.to(DEV), conv.to(DEV), cg, a2.to(DEV), dt_bias.to(DEV), rate_log.to(DEV), g2.to(DEV),
+        K.delta_prepare(*got, first.to(DEV), conv.to(DEV), cg, low2.to(DEV), dt_bias.to(DEV), rate_log.to(DEV),
                         rows_of(counts, slots), dim ** -0.5, 1e-6)
         K.conv_carry(cg, first.to(DEV), c, taps, rows_of(counts, slots))
-        REF.delta_prepare(*want, first, conv, cw, a2, dt_bias, rate_log, g2, rows_of(counts, slots, device="cpu"), dim ** -0.5, 1e-6)
+        REF.delta_prepare(*want, first, conv, cw, low2, dt_bias, rate_log, rows_of(counts, slots, device="cpu"), dim ** -0.5, 1e-6)
         REF.conv_carry(cw, first, c, taps, rows_of(counts, slots, device="cpu"))
         for g, w in zip(got, want):
             close(g, w, torch.float32, scale=8.0)
@@ -136,19 +135,19 @@ def test_delta_prepare_and_the_carried_inputs(K, dtype, heads, kv_heads, dim, vd
 def test_the_convolution_against_its_formula(K):
     """One request fed in portions of 1, 2, 3, 1 and 6 tokens gives the causal convolution of the whole sequence."""
     heads = kv_heads = 1
-    dim, vdim, taps, ra, rg = 8, 8, 4, 2, 2
+    dim, vdim, taps = 8, 8, 4
     c, t = 24, 13
-    x = rand(t, c + heads + ra + rg, seed=1)
+    x = rand(t, c + heads, seed=1)
     conv = rand(c, taps, seed=2)
     want = plain.silu(plain.short_conv(x[:, :c].double(), conv.double()))
     carried = torch.zeros(2, taps - 1, c, device=DEV)
-    rest = [rand(heads * dim, ra, seed=3), rand(heads * dim, seed=4), rand(heads, seed=5), rand(vdim, rg, seed=6)]
+    rest = [rand(heads * dim, seed=4), rand(heads, seed=5)]
     at, got = 0, []
     for n in (1, 2, 3, 1, 6):
         first = x[at:at + n].contiguous().to(DEV)
         out = [torch.empty(s, device=DEV) for s in [(n, 2, 1, dim), (n, 1, vdim), (n, 1), (n, 1, dim), (n, vdim)]]
-        K.delta_prepare(*out, first, conv.to(DEV), carried, rest[0].to(DEV), rest[1].to(DEV), rest[2].to(DEV), rest[3].to(DEV),
-                        rows_of([n], [1]), 1.0, 1e-6)
+        K.delta_prepare(*out, first, conv.to(DEV), carried, torch.zeros(n, heads * dim + vdim, device=DEV), rest[0].to(DEV),
+                        rest[1].to(DEV), rows_of([n], [1]), 1.0, 1e-6)
         K.conv_carry(carried, first, c, taps, rows_of([n], [1]))
         got.append(out[1].view(n, vdim).cpu())
         at += n

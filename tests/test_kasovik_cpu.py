@@ -96,10 +96,10 @@ def test_every_run_has_a_cache_entry_and_state_of_its_own(model):
     for i, layer in enumerate(config["layers"]):
         m = layer["mixer"]
         if layer["type"] == "retention":
-            assert tuple(states[(i, "state")].shape[1:]) == (m["heads"], m["dim"], m["vdim"])
+            assert tuple(states[(i, "state")].shape[1:]) == (m["heads"], m["vdim"], m["dim"])
         else:
             right = m["right"]
-            assert tuple(states[(i, "right.state")].shape[1:]) == (right["heads"], right["dim"], right["vdim"])
+            assert tuple(states[(i, "right.state")].shape[1:]) == (right["heads"], right["vdim"], right["dim"])
             assert ((i, "right.conv") in states) == (right["conv"] > 1)
     assert r.built.cache.prefix is None                   # a state of fixed size cannot be entered in the middle of a prompt
 

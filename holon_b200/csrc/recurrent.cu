@@ -106,6 +106,8 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
 
     fetch(0, 0);
     int which = 0;
+    float o_before = 0.f;                    // the token before's read-out, not yet summed over the column's lanes: its
+    long at_before = -1;                     // sum rides along with this token's S^T k sum, so the two waits overlap
     for (int j0 = 0; j0 < n; j0 += tb, which ^= 1) {
         const int m = min(tb, n - j0);
         if (j0 + tb < n) {
@@ -147,9 +149,16 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 }
                 float a = a0 + a1;
 #pragma unroll
-                for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                for (int o = 1; o < P; o <<= 1) {
+                    a += __shfl_xor_sync(0xffffffffu, a, o);
+                    o_before += __shfl_xor_sync(0xffffffffu, o_before, o);
+                }
                 u = sb[j] * (u - a);
+            } else {
+#pragma unroll
+                for (int o = 1; o < P; o <<= 1) o_before += __shfl_xor_sync(0xffffffffu, o_before, o);
             }
+            if (at_before >= 0 && p == 0 && col) out[((size_t)at_before * heads + h) * vdim + c] = o_before;
             float o0 = 0.f, o1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
@@ -161,13 +170,14 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 o0 = fmaf(S[4 * i], q4.x, o0); o1 = fmaf(S[4 * i + 1], q4.y, o1);
                 o0 = fmaf(S[4 * i + 2], q4.z, o0); o1 = fmaf(S[4 * i + 3], q4.w, o1);
             }
-            float o = o0 + o1;
-#pragma unroll
-            for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-            if (p == 0 && col) out[((size_t)(t0 + j0 + j) * heads + h) * vdim + c] = o;
+            o_before = o0 + o1;
+            at_before = t0 + j0 + j;
         }
         __syncthreads();                                            // this stage is read: the next fetch may fill it
     }
+#pragma unroll
+    for (int x = 1; x < P; x <<= 1) o_before += __shfl_xor_sync(0xffffffffu, o_before, x);
+    if (at_before >= 0 && p == 0 && col) out[((size_t)at_before * heads + h) * vdim + c] = o_before;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
         const int d = ((i >> 2) * P + p) * 4 + (i & 3);

@@ -97,7 +97,7 @@ int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const in
 int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
                                  int rows, int q_tiles, int tokens, int heads, int kv_heads, int head_dim, int pages,
-                                 int page_size, float scale, int window, int tile_q, hb_stream stream);
+                                 int page_size, float scale, int window, int tile_q, const float* sinks, hb_stream stream);
 int hb_attention_tcgen05_status(unsigned int* status);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.

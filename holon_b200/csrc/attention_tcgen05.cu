@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, bf16* __restrict__ out,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
-        int kv_heads, int pages, int page_size, float scale_log2, int window, int tile_q) {
+        int kv_heads, int pages, int page_size, float scale_log2, int window, int tile_q,
+        const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES;
@@ -304,6 +305,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         if (ok) ok = mbar_wait(o_full0 + 8 * g, 0, 9);
         tc_fence_after();
         if (ok && qn > 0) {                                           // (the tensor-memory loads are warp-collective: no lane skips them)
+            if (sinks && l > 0.f) l += at_ex2(fmaf(sinks[h], 1.4426950408889634f, -m_used));   // the sink: a weight without a value
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool keep = r < qn && my_tiles > 0 && l > 0.f;
             bf16* o_row = out + ((size_t)(t0 + g * AT_BM + (r < qn ? r : 0)) * heads + h) * AT_D;
@@ -363,7 +365,7 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
                                             int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                             const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
                                             int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
-                                            int tile_q, hb_stream stream) {
+                                            int tile_q, const float* sinks, hb_stream stream) {
     if (rows <= row0 || q_tiles == 0) return 0;
     if (tile_q != AT_BM && tile_q != AT_GROUPS * AT_BM) HB_REFUSE("attention_prefill_tcgen05: query tiles of %d (128 or 256)", tile_q);
     if (head_dim != AT_D) HB_REFUSE("attention_prefill_tcgen05: head_dim %d; this kernel is for %d", head_dim, AT_D);
@@ -382,7 +384,7 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
     prefill_tcgen05_kernel<<<dim3(heads, q_tiles), AT_THREADS, AT_SMEM, (cudaStream_t)stream>>>(
         map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
-        pages, page_size, scale * 1.4426950408889634f, window, tile_q);
+        pages, page_size, scale * 1.4426950408889634f, window, tile_q, sinks);
     HB_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }

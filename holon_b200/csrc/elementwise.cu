@@ -328,12 +328,51 @@ __global__ void sum_into_kernel(float* __restrict__ h, const T* __restrict__ x0,
     h[i] = a;
 }
 
+// The same, four neighbouring values a thread (hidden a multiple of 4, pointers on 16-byte boundaries).
+template <typename T>
+__global__ void sum_into4_kernel(float* __restrict__ h, const T* __restrict__ x0, const T* __restrict__ x1,
+                                 const T* __restrict__ x2, const T* __restrict__ x3, float s0, float s1, float s2, float s3,
+                                 const T* __restrict__ bias, long quads, int hidden) {
+    const long q = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= quads) return;
+    const long i = q * 4;
+    float a[4], x[4];
+    Vec4<float>::load(h + i, a);
+    const T* terms[4] = {x0, x1, x2, x3};
+    const float scales[4] = {s0, s1, s2, s3};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (terms[k]) {
+            Vec4<T>::load(terms[k] + i, x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) a[e] = fmaf(scales[k], x[e], a[e]);
+        }
+    }
+    if (bias) {
+        Vec4<T>::load(bias + i % hidden, x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[e] += x[e];
+    }
+    Vec4<float>::store(h + i, a);
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 extern "C" int hb_sum_into(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1,
                            float s2, float s3, const void* bias, int dtype, int tokens, int hidden, hb_stream stream) {
     const long count = (long)tokens * hidden;
     if (count == 0) return 0;
-    const unsigned blocks = (unsigned)((count + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
+    if (hidden % 4 == 0 && aligned16(h) && aligned16(x0) && aligned16(x1) && aligned16(x2) && aligned16(x3) && aligned16(bias)
+        && (dtype == HB_F32 || dtype == HB_BF16)) {
+        const long quads = count / 4;
+        const unsigned blocks4 = (unsigned)((quads + 255) / 256);
+        if (dtype == HB_F32) sum_into4_kernel<float><<<blocks4, 256, 0, s>>>(h, (const float*)x0, (const float*)x1, (const float*)x2, (const float*)x3, s0, s1, s2, s3, (const float*)bias, quads, hidden);
+        else sum_into4_kernel<bf16><<<blocks4, 256, 0, s>>>(h, (const bf16*)x0, (const bf16*)x1, (const bf16*)x2, (const bf16*)x3, s0, s1, s2, s3, (const bf16*)bias, quads, hidden);
+        HB_LAUNCH_CHECK("sum_into");
+        return 0;
+    }
+    const unsigned blocks = (unsigned)((count + 255) / 256);
     if (dtype == HB_F32) sum_into_kernel<float><<<blocks, 256, 0, s>>>(h, (const float*)x0, (const float*)x1, (const float*)x2, (const float*)x3, s0, s1, s2, s3, (const float*)bias, count, hidden);
     else if (dtype == HB_BF16) sum_into_kernel<bf16><<<blocks, 256, 0, s>>>(h, (const bf16*)x0, (const bf16*)x1, (const bf16*)x2, (const bf16*)x3, s0, s1, s2, s3, (const bf16*)bias, count, hidden);
     else HB_REFUSE("sum_into: dtype %d", dtype);
@@ -357,12 +396,45 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ ga
     out[t * inter + i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
 }
 
+// The same, four neighbouring values a thread (inter a multiple of 4, pointers on 16-byte boundaries).
+template <typename T>
+__global__ void glu_clamped4_kernel(T* __restrict__ out, const T* __restrict__ gate_up, const T* __restrict__ bias,
+                                    float limit, float alpha, int inter) {
+    const size_t t = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= inter) return;
+    float g[4], u[4], b[4], y[4];
+    Vec4<T>::load(gate_up + t * 2 * inter + i, g);
+    Vec4<T>::load(gate_up + t * 2 * inter + inter + i, u);
+    if (bias) {
+        Vec4<T>::load(bias + i, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) g[e] += b[e];
+        Vec4<T>::load(bias + inter + i, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) u[e] += b[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float ge = fminf(g[e], limit), ue = fminf(fmaxf(u[e], -limit), limit);
+        y[e] = ge / (1.f + expf(-alpha * ge)) * (ue + 1.f);
+    }
+    Vec4<T>::store(out + t * inter + i, y);
+}
+
 extern "C" int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, float limit, float alpha,
                               int tokens, int inter, hb_stream stream) {
     if (tokens == 0 || inter == 0) return 0;
     if (tokens > 65535) HB_REFUSE("glu_clamped: %d rows are above 65535", tokens);
-    dim3 grid((inter + 255) / 256, tokens);
     cudaStream_t s = (cudaStream_t)stream;
+    if (inter % 4 == 0 && aligned16(out) && aligned16(gate_up) && aligned16(bias) && (dtype == HB_F32 || dtype == HB_BF16)) {
+        dim3 grid4((inter / 4 + 255) / 256, tokens);
+        if (dtype == HB_F32) glu_clamped4_kernel<float><<<grid4, 256, 0, s>>>((float*)out, (const float*)gate_up, (const float*)bias, limit, alpha, inter);
+        else glu_clamped4_kernel<bf16><<<grid4, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, (const bf16*)bias, limit, alpha, inter);
+        HB_LAUNCH_CHECK("glu_clamped");
+        return 0;
+    }
+    dim3 grid((inter + 255) / 256, tokens);
     if (dtype == HB_F32) glu_clamped_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)gate_up, (const float*)bias, limit, alpha, inter);
     else if (dtype == HB_BF16) glu_clamped_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, (const bf16*)bias, limit, alpha, inter);
     else HB_REFUSE("glu_clamped: dtype %d", dtype);

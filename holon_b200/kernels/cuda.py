@@ -411,7 +411,7 @@ class CudaKernels:
     def paged_attention(self, out, q, kv, block_table, rows, scale, window, sinks=None) -> None:
         """`sinks` (float32 [heads], or None): a weight exp(sinks[h]) in each head's softmax denominator that has
         neither key nor value. Rows of one token then take the split kernel with its merge kernel (the cluster and the
-        balanced forms do not know sinks), rows of several the mma.sync kernel."""
+        balanced forms do not know sinks); the prompt kernels, generic, mma.sync and tcgen05, all take them."""
         self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len, sinks)
         t, heads, head_dim = q.shape
         if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (heads,)):
@@ -451,12 +451,12 @@ class CudaKernels:
                 self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
                            rows.n_decode, *sizes, splits, self._p(sinks))
         if rows.n_rows > rows.n_decode:
-            if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0 and sinks is None:
+            if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
                 tile_q, tiles = 256, self._query_tiles(rows, 256)
                 if self.prefill_tile == 128 or (self.prefill_tile is None and 4 * heads * tiles < 3 * self.sms):              # tiles of 256 queries would leave SMs idle: one group of
                     tile_q, tiles = 128, self._query_tiles(rows, 128)   # 128 a CTA, twice the CTAs
                 self._call("hb_attention_prefill_tcgen05", self._p(out), self._p(q), self._p(kv), *common,
-                           rows.n_decode, rows.n_rows, tiles, t, *sizes, tile_q)
+                           rows.n_decode, rows.n_rows, tiles, t, *sizes, tile_q, self._p(sinks))
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, self._query_tiles(rows, 64), *sizes, self._p(sinks))

@@ -17,10 +17,6 @@ def rms(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def embedding(w, cfg, tokens):
     """Scaled table rows plus a row of the bigram table chosen by (previous token, token); the first token of a
     sequence takes the table's last row."""

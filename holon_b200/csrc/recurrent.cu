@@ -39,7 +39,7 @@ __device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int DPT, int P>
+template <int DPT, int P, bool PER_CHANNEL, bool DELTA>
 __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qk, const float* __restrict__ v,
                                       const float* __restrict__ decay, const float* __restrict__ head_decay,
                                       const float* __restrict__ beta, float* __restrict__ state,
@@ -54,10 +54,10 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
     const int t0 = query_start[b], n = query_start[b + 1] - t0;
     float* S_g = state + (((size_t)row_slot[b] * heads + h) * vdim + (col ? c : 0)) * dim;   // this thread's column
     // a stage: q [tb][DP], k [tb][DP], decays [tb][DP] (per-channel decays only), v [tb][VT], beta [tb]; two of them
-    const int used = tb * ((decay ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
+    const int used = tb * ((PER_CHANNEL ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
     for (int e = threadIdx.x; e < 2 * per_stage; e += blockDim.x) {      // what no copy fills stays neutral: k = q = v = 0,
         const int at = e % per_stage;                                    // decay = beta = 1
-        const bool one = (decay && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
+        const bool one = (PER_CHANNEL && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
         sm[e] = one ? 1.f : 0.f;
     }
     float S[DPT];
@@ -75,7 +75,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         float* sq = sm + which * per_stage;
         float* sk = sq + tb * DP;
         float* sg = sk + tb * DP;
-        float* sv = sg + (decay ? tb * DP : 0);
+        float* sv = sg + (PER_CHANNEL ? tb * DP : 0);
         float* sb = sv + tb * VT;
         const int m = min(tb, n - j0);
         if (vec) {
@@ -85,7 +85,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 const size_t t = (size_t)(t0 + j0 + j);
                 cp_async_f32x4(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
                 cp_async_f32x4(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
-                if (decay) cp_async_f32x4(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+                if (PER_CHANNEL) cp_async_f32x4(sg + j * DP + d, decay + (t * heads + h) * dim + d);
             }
         } else {
             for (int e = threadIdx.x; e < m * dim; e += blockDim.x) {
@@ -93,14 +93,14 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 const size_t t = (size_t)(t0 + j0 + j);
                 cp_async_f32(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
                 cp_async_f32(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
-                if (decay) cp_async_f32(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+                if (PER_CHANNEL) cp_async_f32(sg + j * DP + d, decay + (t * heads + h) * dim + d);
             }
         }
         for (int e = threadIdx.x; e < m * width; e += blockDim.x) {
             const int j = e / width, x = e - j * width;
             cp_async_f32(sv + j * VT + x, v + ((size_t)(t0 + j0 + j) * heads + h) * vdim + c0 + x);
         }
-        if (beta && (int)threadIdx.x < m) cp_async_f32(sb + threadIdx.x, beta + (size_t)(t0 + j0 + threadIdx.x) * heads + h);
+        if (DELTA && (int)threadIdx.x < m) cp_async_f32(sb + threadIdx.x, beta + (size_t)(t0 + j0 + threadIdx.x) * heads + h);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
@@ -120,8 +120,9 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         const float* sq = sm + which * per_stage;
         const float* sk = sq + tb * DP;
         const float* sg = sk + tb * DP;
-        const float* sv = sg + (decay ? tb * DP : 0);
+        const float* sv = sg + (PER_CHANNEL ? tb * DP : 0);
         const float* sb = sv + tb * VT;
+#pragma unroll 2
         for (int j = 0; j < m; ++j) {
             const float4* kj = (const float4*)(sk + j * DP) + p;    // group i4 of this thread: kj[i4 * P]
             const float4* qj = (const float4*)(sq + j * DP) + p;
@@ -129,7 +130,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
             float4 k4[DPT / 4];
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) k4[i] = kj[i * P];
-            if (decay) {
+            if (PER_CHANNEL) {
                 const float4* gj = (const float4*)(sg + j * DP) + p;
 #pragma unroll
                 for (int i = 0; i < DPT / 4; ++i) {
@@ -140,7 +141,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) S[i] *= fixed;
             }
-            if (beta) {
+            if (DELTA) {
                 float a0 = 0.f, a1 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT / 4; ++i) {
@@ -201,7 +202,8 @@ static int launch_scan(float* out, const float* qk, const float* v, const float*
     if (tb > threads) tb = threads;
     if (most > 0 && tb > most) tb = most;                             // (no row brings more tokens than that)
     const size_t smem = (size_t)2 * ((tb * per_token + 3) & ~3) * sizeof(float);
-    auto kernel = recurrent_scan_kernel<DPT, P>;
+    auto kernel = decay ? (beta ? recurrent_scan_kernel<DPT, P, true, true> : recurrent_scan_kernel<DPT, P, true, false>)
+                        : (beta ? recurrent_scan_kernel<DPT, P, false, true> : recurrent_scan_kernel<DPT, P, false, false>);
     if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<dim3(rows, heads, tiles), threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot,
                                                           heads, kv_heads, dim, vdim, VT, tb);

@@ -204,3 +204,54 @@ def test_the_command_line_serves_the_design(tmp_path, capsys, monkeypatch):
         assert token == int(logits.argmax()) or float(logits.max() - logits[token]) < 1e-4
         ids.append(token)
     assert len(out["token_ids"]) == 4
+
+
+class _Faulty(RefKernels):
+    """The plain kernel table with one fault planted: the comparisons above must notice each of them."""
+
+    def __init__(self, fault: str) -> None:
+        self.fault = fault
+
+    def paged_attention(self, out, q, kv, block_table, rows, scale, window, sinks=None):
+        if self.fault == "no_sink":
+            sinks = None
+        if self.fault == "window_one_more" and window > 0:
+            window += 1
+        if self.fault == "window_one_less" and window > 1:
+            window -= 1
+        super().paged_attention(out, q, kv, block_table, rows, scale, window, sinks)
+
+    def conv_carry(self, conv_state, first, channels, taps, rows):
+        if self.fault != "inputs_not_carried":
+            super().conv_carry(conv_state, first, channels, taps, rows)
+
+    def embed_pair(self, out, table, scale, pair, ids, positions, rows, prev, mul_prev, mul_cur, buckets):
+        keep = prev.clone()
+        super().embed_pair(out, table, scale, pair, ids, positions, rows, prev, mul_prev, mul_cur, buckets)
+        if self.fault == "previous_token_not_carried":
+            prev.copy_(keep)
+
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows):
+        keep = state.clone()
+        super().recurrent_scan(out, qk, v, decay, head_decay, beta, state, rows)
+        if self.fault == "state_not_written":
+            state.copy_(keep)
+
+    def sum_into(self, h, terms, bias=None):
+        super().sum_into(h, terms, None if self.fault == "no_output_bias" else bias)
+
+
+@pytest.mark.parametrize("fault", ["none", "no_sink", "window_one_more", "window_one_less", "inputs_not_carried",
+                                   "previous_token_not_carried", "state_not_written", "no_output_bias"])
+def test_planted_faults_are_noticed(tmp_path, fault):
+    folder = make_folder(tmp_path, "a", seed=5)
+    ids = random_prompt(CONFIGS["a"]["vocab"], 41, 81)
+    want = {"x": exact_logits(folder, ids)}
+    r = Replayer(str(folder), "float32", 64, device="cpu", kernels=_Faulty(fault), page_size=4)
+    parts = portions(ids, [3, 2, 7, 1, 5])
+    got = run(r, [([("x", p)], ["x"] if i == len(parts) - 1 else []) for i, p in enumerate(parts)])
+    if fault == "none":
+        compare(got, want, "float32")
+    else:
+        with pytest.raises(AssertionError):
+            compare(got, want, "float32")

@@ -310,6 +310,11 @@ int hb_embed_pair(float* out, const void* table, int table_dtype, float scale, c
 // h [tokens, hidden] (32-bit) += s0 x0 + s1 x1 + s2 x2 + s3 x3 + bias; terms of `dtype`, any of them null.
 int hb_sum_into(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1, float s2,
                 float s3, const void* bias, int dtype, int tokens, int hidden, hb_stream stream);
+// hb_sum_into, and out [tokens, hidden] (`dtype`) = RMSNorm of the summed rows with `weight` (+ offset): the sum that ends one
+// block and the norm that starts the next in one kernel.
+int hb_sum_norm(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1, float s2,
+                float s3, const void* bias, int dtype, void* out, const void* weight, int weight_dtype, float eps,
+                float offset, int tokens, int hidden, hb_stream stream);
 // out [tokens, inter] = g sigmoid(alpha g) (u + 1), g = min(gate + b, limit), u = clamp(up + b, -limit, limit), from
 // gate_up [tokens, 2 inter] (gate first) and bias [2 inter] (or null).
 int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, float limit, float alpha, int tokens,

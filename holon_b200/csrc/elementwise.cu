@@ -441,3 +441,87 @@ extern "C" int hb_glu_clamped(void* out, const void* gate_up, const void* bias, 
     HB_LAUNCH_CHECK("glu_clamped");
     return 0;
 }
+
+// ---------------------------------------------------------------- the block's sum and the next block's norm in one
+// h[t, :] += sum_i scale_i x_i[t, :] + bias as hb_sum_into, and out[t, :] = h[t, :] rsqrt(mean(h[t, :]^2) + eps)
+// (weight + offset): one block a row, the summed row kept in shared memory between the two passes.
+template <typename T, typename TW, bool VEC>
+__global__ void sum_norm_kernel(float* __restrict__ h, const T* __restrict__ x0, const T* __restrict__ x1,
+                                const T* __restrict__ x2, const T* __restrict__ x3, float s0, float s1, float s2, float s3,
+                                const T* __restrict__ bias, T* __restrict__ out, const TW* __restrict__ weight, float eps,
+                                float offset, int hidden) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    if constexpr (VEC) {                          // four neighbouring values a thread and turn, every load of a turn in flight at once
+        const T* terms[4] = {x0, x1, x2, x3};
+        const float scales[4] = {s0, s1, s2, s3};
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float a[4], x[4][4], b[4] = {0.f, 0.f, 0.f, 0.f};
+            Vec4<float>::load(h + base + i, a);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (terms[k]) Vec4<T>::load(terms[k] + base + i, x[k]);
+            if (bias) Vec4<T>::load(bias + i, b);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (terms[k]) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) a[e] = fmaf(scales[k], x[k][e], a[e]);
+                }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] += b[e]; ss = fmaf(a[e], a[e], ss); }
+            Vec4<float>::store(h + base + i, a);
+            Vec4<float>::store(row + i, a);
+        }
+        const float f = rsqrtf(block_sum(ss, scratch) / hidden + eps);
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float a[4], w[4];
+            Vec4<float>::load(row + i, a);
+            Vec4<TW>::load(weight + i, w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) a[e] = a[e] * f * (w[e] + offset);
+            Vec4<T>::store(out + base + i, a);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float a = h[base + i];
+            if (x0) a = fmaf(s0, to_f32(x0[base + i]), a);
+            if (x1) a = fmaf(s1, to_f32(x1[base + i]), a);
+            if (x2) a = fmaf(s2, to_f32(x2[base + i]), a);
+            if (x3) a = fmaf(s3, to_f32(x3[base + i]), a);
+            if (bias) a += to_f32(bias[i]);
+            h[base + i] = a;
+            row[i] = a;
+            ss = fmaf(a, a, ss);
+        }
+        const float f = rsqrtf(block_sum(ss, scratch) / hidden + eps);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            out[base + i] = from_f32<T>(row[i] * f * (to_f32(weight[i]) + offset));
+    }
+}
+
+extern "C" int hb_sum_norm(float* h, const void* x0, const void* x1, const void* x2, const void* x3, float s0, float s1,
+                           float s2, float s3, const void* bias, int dtype, void* out, const void* weight, int weight_dtype,
+                           float eps, float offset, int tokens, int hidden, hb_stream stream) {
+    if (tokens == 0 || hidden == 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) HB_REFUSE("sum_norm: rows of %d values are more than a block's shared memory holds", hidden);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 2048 ? 512 : 256;
+    const bool vec = hidden % 4 == 0 && aligned16(h) && aligned16(x0) && aligned16(x1) && aligned16(x2) && aligned16(x3)
+        && aligned16(bias) && aligned16(out) && aligned16(weight);
+#define HB_RUN(T, TW) do { \
+        auto kernel = vec ? sum_norm_kernel<T, TW, true> : sum_norm_kernel<T, TW, false>; \
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kernel<<<tokens, threads, smem, s>>>(h, (const T*)x0, (const T*)x1, (const T*)x2, (const T*)x3, s0, s1, s2, s3, \
+                                            (const T*)bias, (T*)out, (const TW*)weight, eps, offset, hidden); } while (0)
+    if (dtype == HB_F32 && weight_dtype == HB_F32) HB_RUN(float, float);
+    else if (dtype == HB_BF16 && weight_dtype == HB_BF16) HB_RUN(bf16, bf16);
+    else if (dtype == HB_BF16 && weight_dtype == HB_F32) HB_RUN(bf16, float);
+    else HB_REFUSE("sum_norm: no kernel for dtype %d with weight dtype %d", dtype, weight_dtype);
+#undef HB_RUN
+    HB_LAUNCH_CHECK("sum_norm");
+    return 0;
+}

@@ -961,6 +961,21 @@ class CudaKernels:
         self._call("hb_sum_into", self._p(h), *(self._p(x) for x in xs), *(ctypes.c_float(sc) for sc in scales),
                    self._p(bias), _code(terms[0][0]), h.shape[0], h.shape[1])
 
+    def sum_norm(self, h, terms, bias, out, weight, eps, offset) -> None:
+        """`sum_into`, and out = RMSNorm(h) · (weight + offset) of the summed rows, in one kernel."""
+        xs = [x for x, _ in terms]
+        self._check(h, bias, out, weight, *xs)
+        if not 1 <= len(terms) <= 4 or h.dtype != torch.float32 or any(x.shape != h.shape or x.dtype != xs[0].dtype for x in xs) \
+                or out.shape != h.shape or out.dtype != xs[0].dtype or weight.shape != (h.shape[1],):
+            raise KernelError("sum_norm: one to four terms and out of h's shape and one dtype, h float32, weight [hidden]")
+        if bias is not None and (bias.shape != (h.shape[1],) or bias.dtype != xs[0].dtype):
+            raise KernelError("sum_norm: bias must be [hidden] of the terms' dtype")
+        xs += [None] * (4 - len(xs))
+        scales = [float(sc) for _, sc in terms] + [0.0] * (4 - len(terms))
+        self._call("hb_sum_norm", self._p(h), *(self._p(x) for x in xs), *(ctypes.c_float(sc) for sc in scales),
+                   self._p(bias), _code(out), self._p(out), self._p(weight), _code(weight), ctypes.c_float(eps),
+                   ctypes.c_float(offset), h.shape[0], h.shape[1])
+
     def glu_clamped(self, out, gate_up, bias, limit, alpha) -> None:
         self._check(out, gate_up, bias)
         if gate_up.shape != (out.shape[0], 2 * out.shape[1]) or out.dtype != gate_up.dtype \

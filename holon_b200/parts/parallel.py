@@ -1,7 +1,9 @@
 """Parts that run side by side on the same input.
 
 `ParallelBlock`: one norm, and mixer and feed-forward both read its output: with h = norm(x), x ← x + mixer(h) +
-ffn(h). The residual sum is one kernel over all terms, in 32-bit, straight into the stream.
+ffn(h). The residual sum is one kernel over all terms, in 32-bit, straight into the stream; where the block that runs
+next is a parallel block too, the same kernel leaves that block's normed rows behind (`Residual.normed`), so a layer
+has one launch for its sum and the next layer's norm.
 
 `SideBySide`: a mixer made of two mixers that read the same input, result = left_scale · left + right_scale · right.
 At most one of the two may ask for a paged cache; their fixed-size states are kept under `left.` and `right.` names.
@@ -85,5 +87,11 @@ class ParallelBlock(Part):
             else:
                 y = self.ffn.forward(x, step)
             terms.append((y, 1.0))
-        self.ctx.kernels.sum_into(stream.h, terms, bias)
+        k, nxt = self.ctx.kernels, getattr(after, "norm", None) if isinstance(after, ParallelBlock) else None
+        if nxt is not None and hasattr(k, "sum_norm"):
+            rows = self.ctx.empty(*stream.h.shape)
+            k.sum_norm(stream.h, terms, bias, rows, nxt.weight.tensor, nxt.eps, nxt.offset)
+            stream.normed, stream.normed_by = rows, nxt
+        else:
+            k.sum_into(stream.h, terms, bias)
         return stream

@@ -124,6 +124,10 @@ class RefKernels:
         if bias is not None:
             h += bias.float()
 
+    def sum_norm(self, h, terms, bias, out, weight, eps, offset):
+        self.sum_into(h, terms, bias)
+        self.rmsnorm(out, h, weight, eps, offset)
+
     def glu_clamped(self, out, gate_up, bias, limit, alpha):
         z = gate_up.float() + (bias.float() if bias is not None else 0.0)
         g, u = z.chunk(2, dim=-1)

@@ -214,6 +214,13 @@ def test_embed_pair_sum_into_and_glu(K, dtype):
         K.sum_into(hg, [(x.to(DEV), s) for x, s in terms[:n]], b.to(DEV) if b is not None else None)
         REF.sum_into(hw, terms[:n], b)
         close(hg, hw, torch.float32, scale=4.0)
+        for gain in (1 + rand(hidden, seed=12) * 0.1, (1 + rand(hidden, seed=12) * 0.1).to(dtype)):      # the sum and the next norm in one
+            hg, hw = h.clone().to(DEV), h.clone()
+            og, ow = torch.empty(11, hidden, dtype=dtype, device=DEV), torch.zeros(11, hidden, dtype=dtype)
+            K.sum_norm(hg, [(x.to(DEV), s) for x, s in terms[:n]], b.to(DEV) if b is not None else None, og, gain.to(DEV), 1e-5, 0.0)
+            REF.sum_norm(hw, terms[:n], b, ow, gain, 1e-5, 0.0)
+            close(hg, hw, torch.float32, scale=4.0)
+            close(og, ow, dtype, scale=4.0)
     inter = 100
     gate_up, b2 = rand(11, 2 * inter, dtype=dtype, seed=10, scale=2.0), rand(2 * inter, dtype=dtype, seed=11)
     for limit, b in ((0.75, b2), (2.0, None)):

@@ -71,7 +71,8 @@ int hb_attention_decode_cluster_capacity(int head_dim, int splits);
 int hb_attention_decode_bf16_cluster(void* out, const void* q, const void* kv, const int32_t* block_table,
                                      int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                      const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
-                                     int page_size, float scale, int window, int splits, hb_stream stream);
+                                     int page_size, float scale, int window, int splits, const float* sinks,
+                                     hb_stream stream);
 
 // The same rows with the keys of all of them shared out evenly over `ctas` CTAs (one wave that fills the GPU): each
 // takes the same number of 64-key tiles, across rows and heads where its stretch crosses them, so rows of any lengths

@@ -385,7 +385,8 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
         bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int heads, int kv_heads,
-        int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window, int splits) {
+        int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window, int splits,
+        const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");   // (this CTA runs: waited for before anybody writes here)
     const int b = blockIdx.x, split = blockIdx.z;                   // the cluster is the z direction: split = rank in it
@@ -435,6 +436,7 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
                 acc += fs * recv_o[s2 * share + i];
                 l += fs * recv_ml[(s2 * g + r) * 2 + 1];
             }
+            if (sinks && l > 0.f) l += ex2(fmaf(sinks[hk * group + g0 + r], 1.4426950408889634f, -mm));   // (maxima in log2 units)
             out[((size_t)t * heads + hk * group + g0 + r) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         }
         return;
@@ -454,6 +456,7 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
             acc += fs * ld_cluster_f32(stage + (r * D_PAD + d) * 4, s2);
             l += fs * ld_cluster_f32(stage + (16 * D_PAD + r * 2 + 1) * 4, s2);
         }
+        if (sinks && l > 0.f) l += ex2(fmaf(sinks[hk * group + g0 + r], 1.4426950408889634f, -mm));
         out[((size_t)t * heads + hk * group + g0 + r) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     }
     __syncwarp();
@@ -578,7 +581,7 @@ template <int D_PAD, int STAGES>
 static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const int32_t* block_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows,
                                  int heads, int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
-                                 int splits, cudaStream_t s) {
+                                 int splits, const float* sinks, cudaStream_t s) {
     auto kernel = decode_cluster_kernel<D_PAD, STAGES>;
     if (decode_cluster_capacity<D_PAD, STAGES>(splits) < 1)          // (sets the kernel's attributes at its first call)
         HB_REFUSE("attention_decode_bf16_cluster: this GPU places no cluster of %d CTAs", splits);
@@ -595,7 +598,7 @@ static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const
     cfg.numAttrs = 1;
     HB_CUDA(cudaLaunchKernelEx(&cfg, kernel, out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, heads,
                                kv_heads, head_dim, pages, page_size, log2_exact(page_size), scale * 1.4426950408889634f,
-                               window, splits));
+                               window, splits, sinks));
     return 0;
 }
 
@@ -614,7 +617,7 @@ extern "C" int hb_attention_decode_bf16_cluster(void* out, const void* q, const 
                                                 int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                                 const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim,
                                                 int pages, int page_size, float scale, int window, int splits,
-                                                hb_stream stream) {
+                                                const float* sinks, hb_stream stream) {
     if (rows == 0) return 0;
     if (head_dim % 16 || head_dim > 256 || head_dim < 16)
         HB_REFUSE("attention_decode_bf16_cluster: head_dim %d is no multiple of 16 up to 256", head_dim);
@@ -624,7 +627,7 @@ extern "C" int hb_attention_decode_bf16_cluster(void* out, const void* q, const 
     if (rows > 65535 * 32) HB_REFUSE("attention_decode_bf16_cluster: %d rows", rows);
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_ARGS (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len, rows, \
-    heads, kv_heads, head_dim, pages, page_size, scale, window, splits, s
+    heads, kv_heads, head_dim, pages, page_size, scale, window, splits, sinks, s
     if (head_dim <= 64) return launch_decode_cluster<64, 4>(HB_ARGS);
     if (head_dim <= 128) return launch_decode_cluster<128, 2>(HB_ARGS);
     return launch_decode_cluster<256, 2>(HB_ARGS);

@@ -410,8 +410,8 @@ class CudaKernels:
 
     def paged_attention(self, out, q, kv, block_table, rows, scale, window, sinks=None) -> None:
         """`sinks` (float32 [heads], or None): a weight exp(sinks[h]) in each head's softmax denominator that has
-        neither key nor value. Rows of one token then take the split kernel with its merge kernel (the cluster and the
-        balanced forms do not know sinks); the prompt kernels, generic, mma.sync and tcgen05, all take them."""
+        neither key nor value. Every kernel takes them but the balanced form for one-token rows (such rows then run
+        with equal cuts, merged in a cluster or by the merge kernel)."""
         self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len, sinks)
         t, heads, head_dim = q.shape
         if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (heads,)):
@@ -441,10 +441,10 @@ class CudaKernels:
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
                 self._call("hb_attention_decode_bf16_balanced", self._p(out), self._p(scratch), self._p(q), self._p(kv),
                            *common, rows.n_decode, *sizes, ctas)
-            elif sinks is None and splits > 1 and (few := self.decode_cluster_splits(rows.n_decode, heads, kv_heads, head_dim,
+            elif splits > 1 and (few := self.decode_cluster_splits(rows.n_decode, heads, kv_heads, head_dim,
                                                                    rows.max_kv, splits)):
                 self._call("hb_attention_decode_bf16_cluster", self._p(out), self._p(q), self._p(kv), *common,
-                           rows.n_decode, *sizes, few)
+                           rows.n_decode, *sizes, few, self._p(sinks))
             else:
                 floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None

@@ -4,6 +4,7 @@
     python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
     python -m holon_b200.kernels.microbench prefill_attention [--rows 2048] [--context 2048]
     python -m holon_b200.kernels.microbench layer [--rows 8 1 16 64] [--context 8192]
+    python -m holon_b200.kernels.microbench scan [--rows 2048 256 1] [--heads 16 --kv-heads 4 --dim 128 --vdim 128]
 
 `layer` times the kernels of a decode layer the way a step runs them: back to back inside a CUDA graph, each launch
 on weights (or a cache) other than the launch before, several hundred MB in turn, so that nothing comes from the L2
@@ -81,7 +82,7 @@ def decode_attention(k, args) -> None:
             direct = lambda: k._call(                      # noqa: E731
                 "hb_attention_decode_bf16_cluster", k._p(out), k._p(q), k._p(kv), k._i32(table, "table"), table.shape[1],
                 k._i32(batch.row_slot, "slot"), k._i32(batch.query_start, "start"), k._i32(batch.kv_len, "len"), rows,
-                heads, kv_heads, d, kv.shape[0], page, ctypes.c_float(1 / math.sqrt(d)), 0, splits)
+                heads, kv_heads, d, kv.shape[0], page, ctypes.c_float(1 / math.sqrt(d)), 0, splits, k._p(None))
             t = timed(direct, flush)
             print(f"decode attention rows {rows} context {args.context} a cluster of {splits} splits: {t:7.1f} us  "
                   f"{moved / t / 1e6:5.2f} TB/s")
@@ -383,9 +384,39 @@ def layer(k, args) -> None:
     print("status", k.tcgen05_status())
 
 
+def scan(k, args) -> None:
+    """The scan over a matrix state per head (`recurrent_scan`): one row of `--rows` tokens (1: eight rows of one token),
+    with the delta rule and a decay per key channel, and with one fixed decay per head."""
+    heads, kvh, dim, vdim = args.heads, args.kv_heads, args.dim, args.vdim
+    dev = k.device
+    for tokens in args.rows:
+        counts = [1] * 8 if tokens == 1 else [tokens]
+        t = sum(counts)
+        starts = torch.tensor([sum(counts[:i]) for i in range(len(counts) + 1)], dtype=torch.int32, device=dev)
+        rows = Rows(torch.arange(len(counts), dtype=torch.int32, device=dev), starts, starts[1:].clone(), len(counts), t,
+                    sum(1 for n in counts if n == 1), max(counts), max(counts))
+        for delta in (True, False):
+            qk = torch.randn(t, 2, kvh if delta else heads, dim, device=dev) * 0.05
+            v = torch.randn(t, heads, vdim, device=dev)
+            decay = torch.rand(t, heads, dim, device=dev) * 0.1 + 0.9 if delta else None
+            fixed = None if delta else torch.full((heads,), 0.99, device=dev)
+            beta = torch.rand(t, heads, device=dev) if delta else None
+            state = torch.zeros(len(counts), heads, vdim, dim, device=dev)
+            out = torch.empty(t, heads, vdim, device=dev)
+            us = timed(lambda: k.recurrent_scan(out, qk, v, decay, fixed, beta, state, rows), None)
+            moved = 2 * state.numel() * 4 + (qk.numel() + 2 * v.numel() + (decay.numel() if delta else 0)) * 4
+            print(f"scan {len(counts)} row(s) of {counts[0]:5d} tokens, {heads} heads of {dim} x {vdim}, "
+                  f"{'delta rule' if delta else 'fixed decay'}: {us:8.1f} us  ({us / counts[0]:6.3f} us a token, "
+                  f"{moved / 1e6:6.1f} MB moved)")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention", "chain", "layer"))
+    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention", "chain", "layer", "scan"))
+    ap.add_argument("--heads", type=int, default=16, help="scan: value heads")
+    ap.add_argument("--kv-heads", type=int, default=4, help="scan: query/key heads of the delta rule")
+    ap.add_argument("--dim", type=int, default=128, help="scan: key size")
+    ap.add_argument("--vdim", type=int, default=128, help="scan: value size")
     ap.add_argument("--rows", type=int, nargs="*", default=None)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--splits", type=int, nargs="*", default=None)
@@ -407,6 +438,9 @@ def main() -> None:
         elif args.what == "prefill_attention":
             args.rows = args.rows or [2048]
             prefill_attention(k, args)
+        elif args.what == "scan":
+            args.rows = args.rows or [2048, 256, 1]
+            scan(k, args)
         else:
             args.rows = args.rows or [2048]
             gemm(k, args)

@@ -299,15 +299,20 @@ def test_attention_with_a_sink_at_the_window_s_edges(K, dtype, heads, kv_heads, 
     close(twin, want, dtype, scale=4.0)
 
 
+@pytest.mark.parametrize("cluster", [False, True])
 @pytest.mark.parametrize("splits", [1, 3, 8])
-def test_one_token_rows_with_a_sink_in_parts(K, splits, monkeypatch):
-    """The keys of a one-token row cut into parts that a second kernel merges: the sink enters the denominator once."""
+def test_one_token_rows_with_a_sink_in_parts(K, splits, cluster, monkeypatch):
+    """The keys of a one-token row cut into parts, merged by a second kernel or inside a thread-block cluster: the sink
+    enters the denominator once."""
     heads, kv_heads, d, window, n = 4, 2, 64, 0, 700
     keys, values, q = rand(n, kv_heads, d, dtype=torch.bfloat16, seed=1), rand(n, kv_heads, d, dtype=torch.bfloat16, seed=2), rand(1, heads, d, dtype=torch.bfloat16, seed=3)
     sink = torch.tensor([4.0, 2.0, 0.0, 5.0])
     want = _attend(q.float(), keys.float(), values.float(), 0.2, window, sink)
     kv, table = _paged(keys, values, 64, torch.bfloat16)
     monkeypatch.setattr(K, "decode_splits", lambda *a, **k: splits)
+    monkeypatch.setattr(K, "decode_cluster", cluster)
+    if cluster:
+        monkeypatch.setattr(K, "decode_cluster_splits", lambda *a, **k: splits if splits > 1 else 0)
     out = torch.empty(1, heads, d, dtype=torch.bfloat16, device=DEV)
     K.paged_attention(out, q.to(DEV), kv.to(DEV), table.to(DEV), rows_of([1], [0], kv_len=[n]), 0.2, window, sink.to(DEV))
     close(out, want, torch.bfloat16)

@@ -609,7 +609,7 @@ def test_decode_attention_merged_inside_a_cluster(K, geometry):
             K._call("hb_attention_decode_bf16_cluster", K._p(out), K._p(args[0]), K._p(args[1]), K._i32(args[2], "table"),
                     args[2].shape[1], K._i32(args[3].row_slot, "slot"), K._i32(args[3].query_start, "start"),
                     K._i32(args[3].kv_len, "len"), len(spec), heads, kv_heads, head_dim, kv.shape[0], page,
-                    ctypes.c_float(scale), 0, splits)
+                    ctypes.c_float(scale), 0, splits, K._p(None))
             outs.append(out)
         close(outs[0], want, torch.bfloat16, scale=4)
         assert torch.equal(outs[0], outs[1]), splits

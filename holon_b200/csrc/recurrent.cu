@@ -54,12 +54,6 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
     const int t0 = query_start[b], n = query_start[b + 1] - t0;
     float* S_g = state + (((size_t)row_slot[b] * heads + h) * vdim + (col ? c : 0)) * dim;   // this thread's column
     // a stage: q [tb][DP], k [tb][DP], decays [tb][DP] (per-channel decays only), v [tb][VT], beta [tb]; two of them
-    const int used = tb * ((PER_CHANNEL ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
-    for (int e = threadIdx.x; e < 2 * per_stage; e += blockDim.x) {      // what no copy fills stays neutral: k = q = v = 0,
-        const int at = e % per_stage;                                    // decay = beta = 1
-        const bool one = (PER_CHANNEL && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
-        sm[e] = one ? 1.f : 0.f;
-    }
     float S[DPT];
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
@@ -68,6 +62,63 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
     }
     const float fixed = head_decay ? head_decay[h] : 1.f;
     const bool vec = (dim & 3) == 0;
+    if (n == 1) {                            // a row of one token (a decode step): no stage, no barrier; every thread reads
+        const size_t t = (size_t)t0;         // its own channels of k, q and the decays straight from global memory
+        auto four = [&](const float* base, int d, float fill) -> float4 {
+            if (vec && d + 3 < dim) return *(const float4*)(base + d);
+            return make_float4(d < dim ? base[d] : fill, d + 1 < dim ? base[d + 1] : fill, d + 2 < dim ? base[d + 2] : fill,
+                               d + 3 < dim ? base[d + 3] : fill);
+        };
+        const float* q_g = qk + ((t * 2) * kv_heads + hk) * dim;
+        const float* k_g = qk + ((t * 2 + 1) * kv_heads + hk) * dim;
+        float u = col ? v[(t * heads + h) * vdim + c] : 0.f;
+        float4 k4[DPT / 4], q4[DPT / 4];
+#pragma unroll
+        for (int i = 0; i < DPT / 4; ++i) {
+            const int d = (i * P + p) * 4;
+            k4[i] = four(k_g, d, 0.f);
+            q4[i] = four(q_g, d, 0.f);
+            if (PER_CHANNEL) {
+                const float4 g = four(decay + (t * heads + h) * dim, d, 1.f);
+                S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
+            } else {
+                S[4 * i] *= fixed; S[4 * i + 1] *= fixed; S[4 * i + 2] *= fixed; S[4 * i + 3] *= fixed;
+            }
+        }
+        if (DELTA) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i)
+                a += S[4 * i] * k4[i].x + S[4 * i + 1] * k4[i].y + S[4 * i + 2] * k4[i].z + S[4 * i + 3] * k4[i].w;
+#pragma unroll
+            for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            u = beta[t * heads + h] * (u - a);
+        }
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT / 4; ++i) {
+            S[4 * i] = fmaf(k4[i].x, u, S[4 * i]);
+            S[4 * i + 1] = fmaf(k4[i].y, u, S[4 * i + 1]);
+            S[4 * i + 2] = fmaf(k4[i].z, u, S[4 * i + 2]);
+            S[4 * i + 3] = fmaf(k4[i].w, u, S[4 * i + 3]);
+            o += S[4 * i] * q4[i].x + S[4 * i + 1] * q4[i].y + S[4 * i + 2] * q4[i].z + S[4 * i + 3] * q4[i].w;
+        }
+#pragma unroll
+        for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+        if (p == 0 && col) out[(t * heads + h) * vdim + c] = o;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = ((i >> 2) * P + p) * 4 + (i & 3);
+            if (col && d < dim) S_g[d] = S[i];
+        }
+        return;
+    }
+    const int used = tb * ((PER_CHANNEL ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
+    for (int e = threadIdx.x; e < 2 * per_stage; e += blockDim.x) {      // what no copy fills stays neutral: k = q = v = 0,
+        const int at = e % per_stage;                                    // decay = beta = 1
+        const bool one = (PER_CHANNEL && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
+        sm[e] = one ? 1.f : 0.f;
+    }
     const int width = min(VT, vdim - c0);
     __syncthreads();
 

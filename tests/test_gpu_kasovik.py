@@ -270,7 +270,8 @@ def _attend(q, keys, values, scale, window, sink):
                                                                (4, 4, 128, 100, 400, 1, 64), (4, 4, 128, 100, 400, 150, 64), (2, 2, 48, 1000, 700, 1, 64)])
 def test_attention_with_a_sink_at_the_window_s_edges(K, dtype, heads, kv_heads, d, window, n, nq, page):
     """The last query's key just inside the window and the key just outside it both point along the query, far more than
-    any other: the inner one must take the weight, the outer one none; the sink takes a visible share. Rows of one token
+    any other: the inner one must take the weight, the outer one none (where the window is longer than the row, the
+    fourth key of 700 stands out instead); the sink takes a visible share. Rows of one token
     (the split kernel and its merge), of several (the prompt kernel), head sizes the tensor cores take and others."""
     keys, values = rand(n, kv_heads, d, seed=1), rand(n, kv_heads, d, seed=2)
     q = rand(nq, heads, d, seed=3)
@@ -279,6 +280,8 @@ def test_attention_with_a_sink_at_the_window_s_edges(K, dtype, heads, kv_heads, 
     direction = q[-1, 0] / q[-1, 0].norm()
     if inside >= 0:
         keys[inside, 0] = 3.0 * direction * d ** 0.5 / 2
+    else:                                               # the window is longer than the row: a far key among hundreds
+        keys[3, 0] = 3.0 * direction * d ** 0.5 / 2
     if outside >= 0:
         keys[outside, 0] = 6.0 * direction * d ** 0.5 / 2
     keys, values, q = keys.to(dtype), values.to(dtype), q.to(dtype)

@@ -67,6 +67,11 @@ KC = _model(128, 300, 1e-5, 1.0, (211, 31, 7), [_LC, _RC])
 # One mechanism alone.
 K_RET = _model(48, 97, 1e-5, 1.5, (31, 7, 3), [_retention(3, 16, 16, [0.8, 0.9, 0.99], 100.0, 16, None)])
 K_PAR = _model(48, 97, 1e-5, 1.5, (31, 7, 3), [_parallel(_window(2, 1, 16, 6, 3.0), _delta(2, 1, 16, 24, 3, 4, 4), 0.9, 1.1, None)])
+# D (GPU tests only): attention heads of 128 (the tcgen05 prompt kernel, with window and sink), key sizes 128, 256 and 512 in
+# the scan (8 and 16 key channels a thread), a layer on shared weights.
+_LD = _parallel(_window(4, 2, 128, 100, 5.0), _delta(4, 2, 128, 128, 4, 16, 16), 0.9, 1.2, _mlp(384, 1.0))
+KD = _model(256, 700, 1e-5, 2.0, (509, 29, 5), [_LD, _retention(2, 256, 64, [0.98, 0.999], 1e6, 64, _mlp(384, 1.0)),
+                                                dict(_LD, weights_of=0), _retention(1, 512, 32, [0.995], 1e4, 512, None)])
 CONFIGS = {"a": KA, "b": KB, "c": KC, "ret": K_RET, "par": K_PAR}
 
 

@@ -376,6 +376,29 @@ def test_long_decoding_and_the_first_tokens(model, dtype):
     compare(got, want, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_heads_of_128_and_large_key_sizes(tmp_path, dtype):
+    """Whole prompts of 300 and 133 tokens (the tcgen05 prompt attention with a window of 100 and a sink), their last 32
+    tokens one by one, and portions, at sizes where a thread of the scan holds 8 and 16 key channels."""
+    from kasovik_tools import KD
+    folder = make_folder(tmp_path, "d", seed=3, config=KD)
+    prompts = {f"r{i}": random_prompt(KD["vocab"], n, 50 + i) for i, n in enumerate((300, 133))}
+    want = {rid: exact_logits(folder, ids) for rid, ids in prompts.items()}
+    r = Replayer(str(folder), dtype, max_tokens=512)
+    compare(run(r, [([(rid, ids)], [rid]) for rid, ids in prompts.items()]), want, dtype)
+    steps = []
+    for rid, ids in prompts.items():
+        cut = len(ids) - 32
+        steps.append(([(rid, ids[:cut])], []))
+        steps += [([(rid, [t])], [rid] if i == 31 else []) for i, t in enumerate(ids[cut:])]
+    compare(run(r, steps), want, dtype)
+    steps = []
+    for rid, ids in prompts.items():
+        parts = portions(ids, [7, 2, 130, 3, 64])
+        steps += [([(rid, p)], [rid] if i == len(parts) - 1 else []) for i, p in enumerate(parts)]
+    compare(run(r, steps), want, dtype)
+
+
 def test_a_token_far_back_is_remembered(tmp_path):
     """The matrix states must carry a token from 300 places back: the logits of the last rows change when token 7
     changes, and the engine follows the plain implementation through that change, in a prompt and in decoding, with the
